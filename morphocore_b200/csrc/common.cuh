@@ -1,0 +1,199 @@
+// Shared device / host helpers of the sm_100a morphology kernels.
+//
+// Tiling used by every tile kernel in this folder: a CTA of 256 threads owns a 64 x 32 tile of output
+// pixels of one image plane; thread (tx, ty) = (tid % 16, tid / 16) owns the 4 x 2 pixel patch at
+// columns 4 tx .. 4 tx + 3 and rows 2 ty, 2 ty + 1, so its window rows are read from shared memory
+// with conflict-free 128-bit loads. The shared window of a tile holds the tile plus the halo of the
+// structuring element with the border already resolved:
+//     window row r    <-> image row  tile_h0 - (kH - 1 - kH/2) + r
+//     window column c <-> image col  tile_w0 - (kW - 1 - kW/2) + c
+// so that tap (kh, kw) of the output pixel at tile offset (y, x) reads window (y + kH-1-kh, x + kW-1-kw),
+// which is image pixel (h + kH/2 - kh, w + kW/2 - kw): the reference's tap convention
+// (morphocore/functional/csrc/cuda/morpho_cuda_common.cuh:19, csrc/cpp/morpho_op_cpu_kernels.hxx:256-265).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <limits>
+
+#include "../../include/morphocore_b200.h"
+
+namespace mc
+{
+
+constexpr int TILE_W = 64;
+constexpr int TILE_H = 32;
+constexpr int THREADS = 256;
+constexpr int PATCH_W = 4;  // output pixels per thread along a row
+constexpr int PATCH_H = 2;  // output rows per thread
+
+/// Registers per thread row segment: the patch plus the kernel width, rounded up to whole 128-bit loads.
+__host__ __device__ constexpr int segment_len(int kw, int elem_bytes)
+{
+    const int per_vec = 16 / elem_bytes;
+    return (PATCH_W + kw - 1 + per_vec - 1) / per_vec * per_vec;
+}
+
+/// Row stride of the shared window, in elements: every thread may read a whole segment.
+__host__ __device__ constexpr int window_stride(int kw, int elem_bytes)
+{
+    return TILE_W - PATCH_W + segment_len(kw, elem_bytes);
+}
+
+struct Geometry
+{
+    int B, Ci, Co, H, W, kH, kW;
+    int pH, pW;        // kH / 2, kW / 2
+    int tiles_x, tiles_y;
+    int win_rows;      // TILE_H + kH - 1
+    int win_stride;    // window_stride(kW)
+    int64_t weight_batch_stride;
+    bool replicate;
+    bool identity;
+
+    __host__ __device__ int taps() const { return kH * kW; }
+    __host__ __device__ int64_t plane() const { return static_cast<int64_t>(H) * W; }
+    __host__ __device__ int window_elems() const { return win_rows * win_stride; }
+    __host__ __device__ int halo_top() const { return kH - 1 - pH; }
+    __host__ __device__ int halo_left() const { return kW - 1 - pW; }
+};
+
+inline Geometry make_geometry(const mc_desc& d, int elem_bytes)
+{
+    Geometry g;
+    g.B = d.B; g.Ci = d.Ci; g.Co = d.Co; g.H = d.H; g.W = d.W; g.kH = d.kH; g.kW = d.kW;
+    g.pH = d.kH / 2; g.pW = d.kW / 2;
+    g.tiles_x = (d.W + TILE_W - 1) / TILE_W;
+    g.tiles_y = (d.H + TILE_H - 1) / TILE_H;
+    g.win_rows = TILE_H + d.kH - 1;
+    g.win_stride = window_stride(d.kW, elem_bytes);
+    g.weight_batch_stride = d.weight_batch_stride;
+    g.replicate = d.pad_kind == MC_PAD_REPLICATE;
+    g.identity = d.merge == MC_MERGE_IDENTITY;
+    return g;
+}
+
+template <typename T> struct Limits;
+template <> struct Limits<float>
+{
+    __host__ __device__ static constexpr float inf() { return __builtin_huge_valf(); }
+    __host__ __device__ static constexpr float max() { return 3.402823466e+38f; }
+};
+template <> struct Limits<double>
+{
+    __host__ __device__ static constexpr double inf() { return __builtin_huge_val(); }
+    __host__ __device__ static constexpr double max() { return 1.7976931348623157e+308; }
+};
+
+/// Stage the window of one image plane into shared memory, border resolved: REPLICATE clamps to the edge
+/// pixel, otherwise out-of-image elements read `outside` (the fill value, or NaN for smorph).
+/// Warps take rows, lanes take columns, so global reads are coalesced. Columns past the last one a tap
+/// can reach are set to `outside` too.
+template <typename T>
+__device__ __forceinline__ void load_window(T* __restrict__ dst, const T* __restrict__ plane, const Geometry& g, int tile_h0, int tile_w0,
+                                            T outside)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
+    for (int r = warp; r < g.win_rows; r += THREADS / 32)
+    {
+        const int iy = row0 + r;
+        const bool row_in = iy >= 0 && iy < g.H;
+        const int cy = min(max(iy, 0), g.H - 1);
+        const T* src = plane + static_cast<int64_t>(cy) * g.W;
+        T* out = dst + r * g.win_stride;
+        for (int c = lane; c < g.win_stride; c += 32)
+        {
+            const int ix = col0 + c;
+            const bool in = row_in && ix >= 0 && ix < g.W;
+            T v = outside;
+            if (in || g.replicate) v = __ldg(src + min(max(ix, 0), g.W - 1));
+            out[c] = v;
+        }
+    }
+}
+
+/// One 128-bit shared load of 16 / sizeof(T) consecutive elements.
+__device__ __forceinline__ void lds128(float* dst, const float* src)
+{
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+}
+__device__ __forceinline__ void lds128(double* dst, const double* src)
+{
+    const double2 v = *reinterpret_cast<const double2*>(src);
+    dst[0] = v.x; dst[1] = v.y;
+}
+
+/// Load a thread's row segment of LEN elements (LEN a multiple of the 128-bit vector) from shared memory.
+template <int LEN, typename T>
+__device__ __forceinline__ void load_segment(T (&dst)[LEN], const T* src)
+{
+    constexpr int PER = 16 / sizeof(T);
+#pragma unroll
+    for (int v = 0; v < LEN / PER; v++) lds128(&dst[v * PER], src + v * PER);
+}
+
+// max / min with "the other operand when one is NaN" semantics, like the reference's strict
+// comparison from an initial value that is never NaN.
+template <bool IS_MIN> __device__ __forceinline__ float ext2(float a, float b) { return IS_MIN ? fminf(a, b) : fmaxf(a, b); }
+template <bool IS_MIN> __device__ __forceinline__ double ext2(double a, double b) { return IS_MIN ? fmin(a, b) : fmax(a, b); }
+
+/// Three-input max / min: one sm_100 instruction for two taps.
+template <bool IS_MIN> __device__ __forceinline__ float ext3(float a, float b, float c)
+{
+    float d;
+    if (IS_MIN) asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    else asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+template <bool IS_MIN> __device__ __forceinline__ double ext3(double a, double b, double c) { return ext2<IS_MIN>(ext2<IS_MIN>(a, b), c); }
+
+template <bool IS_MIN, typename T> __device__ __forceinline__ bool strictly_better(T v, T best) { return IS_MIN ? v < best : v > best; }
+
+/// Value of input pixel (iy, ix) of a plane under the border rule, for the per-pixel re-scans.
+template <typename T>
+__device__ __forceinline__ T read_border(const T* __restrict__ plane, const Geometry& g, int iy, int ix, T fill)
+{
+    const bool in = iy >= 0 && iy < g.H && ix >= 0 && ix < g.W;
+    if (!in && !g.replicate) return fill;
+    return __ldg(plane + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W + min(max(ix, 0), g.W - 1));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+void set_last_error(const char* fmt, ...);
+void count_launch();
+
+/// Opt in to more than 48 KiB of dynamic shared memory for a kernel; returns false if the device refuses.
+template <typename K> inline bool allow_shared(K kernel, size_t bytes)
+{
+    if (bytes <= 48 * 1024) return true;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) == cudaSuccess;
+}
+
+constexpr size_t MAX_SHARED_BYTES = 227 * 1024;
+
+inline int check_launch(const char* what)
+{
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess)
+    {
+        set_last_error("%s: %s", what, cudaGetErrorString(err));
+        return MC_ERR_CUDA;
+    }
+    count_launch();
+    return MC_OK;
+}
+
+// Entry points of the translation units, called by api.cu after validation.
+template <typename T> int morpho_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx, cudaStream_t stream);
+template <typename T> int morpho_backward(const mc_desc& d, const T* x, const T* w, const int32_t* idx, const T* gy, T* gx, T* gw, void* ws,
+                                          cudaStream_t stream);
+template <typename T> int smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, T* y, T* counts, cudaStream_t stream);
+template <typename T> int smorph_backward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* y, const T* gy, T* gx, T* gw,
+                                          T* galpha, void* ws, cudaStream_t stream);
+
+}  // namespace mc

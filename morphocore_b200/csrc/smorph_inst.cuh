@@ -1,0 +1,54 @@
+// Instantiates mc::smorph_forward<MC_T> and mc::smorph_backward<MC_T>; included by smorph_f32.cu / _f64.cu.
+#include <type_traits>
+
+#include "dispatch.cuh"
+#include "smorph.cuh"
+
+namespace mc
+{
+
+template <>
+int smorph_forward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const MC_T* alpha, MC_T* y, MC_T* counts, cudaStream_t stream)
+{
+    using T = MC_T;
+    // Stats mode (counts != nullptr) reads y as the merge target instead of writing it.
+    const T* target = counts != nullptr ? y : nullptr;
+    const bool wide = d.merge != MC_MERGE_IDENTITY && d.Co >= 2;
+    return dispatch_kernel_width(d.kW, [&](auto kw) {
+        constexpr int KW = decltype(kw)::value;
+        return wide ? launch_smorph_forward<T, KW, 2>(d, x, w, alpha, y, target, counts, stream)
+                    : launch_smorph_forward<T, KW, 1>(d, x, w, alpha, y, target, counts, stream);
+    });
+}
+
+template <>
+int smorph_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const MC_T* alpha, const MC_T* y, const MC_T* gy, MC_T* gx, MC_T* gw,
+                          MC_T* galpha, void* ws, cudaStream_t stream)
+{
+    using T = MC_T;
+    const size_t taps = static_cast<size_t>(d.kH) * d.kW;
+    const bool identity = d.merge == MC_MERGE_IDENTITY;
+    const size_t wnumel = static_cast<size_t>(d.Co) * (identity ? 1 : d.Ci) * taps;
+    const size_t anumel = identity ? d.Co : static_cast<size_t>(d.Co) * d.Ci;
+    if (cudaMemsetAsync(gx, 0, sizeof(T) * static_cast<size_t>(d.B) * d.Ci * d.H * d.W, stream) != cudaSuccess
+        || cudaMemsetAsync(gw, 0, sizeof(T) * wnumel, stream) != cudaSuccess
+        || cudaMemsetAsync(galpha, 0, sizeof(T) * anumel, stream) != cudaSuccess)
+    {
+        set_last_error("cudaMemsetAsync: %s", cudaGetErrorString(cudaGetLastError()));
+        return MC_ERR_CUDA;
+    }
+    const T* counts = nullptr;
+    if (d.merge == MC_MERGE_MAX || d.merge == MC_MERGE_MIN)
+    {
+        // Winners per output pixel, from one more pass over every channel.
+        const int rc = smorph_forward<T>(d, x, w, alpha, const_cast<T*>(y), static_cast<T*>(ws), stream);
+        if (rc != MC_OK) return rc;
+        counts = static_cast<const T*>(ws);
+    }
+    return dispatch_kernel_width(d.kW, [&](auto kw) {
+        constexpr int KW = decltype(kw)::value;
+        return launch_smorph_backward<T, KW>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
+    });
+}
+
+}  // namespace mc
