@@ -348,15 +348,19 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_backwa
         T ref[PATCH_H][PATCH_W], sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
         smorph_pair<KW>(sx, sw, 1, s, scale, g, tx, ty, ref, sum, out);
 
+        // scaled = g / S for the pixels of the image; pixels of a partial tile that lie outside it are
+        // dead: their forward state may be inf or NaN and must not reach any sum.
         T scaled[PATCH_H][PATCH_W];
+        bool live[PATCH_H][PATCH_W];
 #pragma unroll
         for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
             for (int j = 0; j < PATCH_W; j++)
             {
                 const int h = tile_h0 + ty * PATCH_H + rr, w = tile_w0 + tx * PATCH_W + j;
+                live[rr][j] = h < g.H && w < g.W;
                 T grad = T(0);
-                if (h < g.H && w < g.W)
+                if (live[rr][j])
                 {
                     const int64_t at = ((static_cast<int64_t>(b) * g.Co + o) * g.H + h) * g.W + w;
                     grad = __ldg(a.gy + at) * a.scale;
@@ -368,7 +372,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_backwa
                         if (!(dist < T(1e-6) && dist > -T(1e-6))) grad = T(0);
                     }
                 }
-                scaled[rr][j] = grad * (T(1) / sum[rr][j]);
+                scaled[rr][j] = live[rr][j] ? grad * (T(1) / sum[rr][j]) : T(0);
             }
 
         T alpha_sum = T(0);
@@ -388,12 +392,11 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_backwa
                 current = k;
             }
             const T u = fma(s, xv, sw[k]);
-            const bool valid = u == u;
-            const T uu = valid ? u : ref[rr][j];
-            const T d = uu - ref[rr][j];
+            const bool valid = u == u && live[rr][j];  // the tap reads a pixel of the image, for a pixel of the image
+            const T d = valid ? u - ref[rr][j] : T(0);
             const T e = valid ? soft_exp(d, scale) : T(0);
             const T pg = e * scaled[rr][j];
-            const T centered = uu - out[rr][j];
+            const T centered = valid ? u - out[rr][j] : T(0);
             const T c = fma(abs_alpha * pg, centered, pg);
             if (c != T(0))
             {

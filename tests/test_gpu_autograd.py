@@ -1,0 +1,172 @@
+"""The public Python surface on the GPU: functional calls and modules through torch.ops.morphocore,
+autograd, gradcheck, shapes, errors, and config 5 (the 4-layer training step) against the fixture."""
+import numpy as np
+import pytest
+import torch
+
+import workloads as WL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def F():
+    import morphocore_b200.functional as F
+    return F
+
+
+def test_public_api_matches_golden_gradients(F, manifest, golden):
+    """User-level gradients (erosion's un-flipped grad_weight; smorph's gradients through the tanh
+    re-parametrisation) against the reference's."""
+    data = golden("morph_small")
+    for case in manifest["morph_small"][::3]:
+        k = case["key"]
+        x = torch.from_numpy(data[k + "_x"]).cuda().requires_grad_(True)
+        w = torch.from_numpy(data[k + "_w"]).cuda().requires_grad_(True)
+        fn = F.dilation if case["op"] == "dilation" else F.erosion
+        y = fn(x, w, case["merge"], case["padding"], padding_value=case["padding_value"])
+        assert np.array_equal(y.detach().cpu().numpy(), data[k + "_y"])
+        y.backward(torch.from_numpy(data[k + "_gy"]).cuda())
+        tol = dict(rtol=1e-4, atol=1e-4) if x.dtype == torch.float32 else dict(rtol=1e-11, atol=1e-11)
+        np.testing.assert_allclose(x.grad.cpu().numpy(), data[k + "_gx"], **tol)
+        np.testing.assert_allclose(w.grad.cpu().numpy(), data[k + "_gw"], **tol)
+    data = golden("smorph_small")
+    for case in manifest["smorph_small"]:
+        if abs(case["alpha0"]) >= 100:
+            continue
+        k = case["key"]
+        x, w, a = (torch.from_numpy(data[k + n]).cuda().requires_grad_(True) for n in ("_x", "_w", "_alpha"))
+        y = F.smorph(x, w, a, channel_merge_mode=case["merge"])
+        y.backward(torch.from_numpy(data[k + "_gy"]).cuda())
+        tol = dict(rtol=1e-4, atol=3e-4) if x.dtype == torch.float32 else dict(rtol=1e-9, atol=1e-10)
+        np.testing.assert_allclose(y.detach().cpu().numpy(), data[k + "_y"], rtol=tol["rtol"], atol=1e-5 if x.dtype == torch.float32 else 1e-11)
+        np.testing.assert_allclose(x.grad.cpu().numpy(), data[k + "_gx"], **tol)
+        np.testing.assert_allclose(w.grad.cpu().numpy(), data[k + "_gw"], **tol)
+        np.testing.assert_allclose(a.grad.cpu().numpy(), data[k + "_galpha"], rtol=tol["rtol"], atol=tol["atol"] * 10)
+
+
+@pytest.mark.parametrize("merge", ["sum", "mean", "max", "min", "identity"])
+@pytest.mark.parametrize("op", ["dilation", "erosion"])
+def test_gradcheck_morph(F, op, merge):
+    torch.manual_seed(0)
+    fn = F.dilation if op == "dilation" else F.erosion
+    c = 3
+    x = torch.randn(2, c, 6, 7, dtype=torch.float64, device="cuda", requires_grad=True)
+    w = torch.randn(c if merge == "identity" else 2, 1 if merge == "identity" else c, 3, 3, dtype=torch.float64, device="cuda", requires_grad=True)
+    for save in (True, False):
+        assert torch.autograd.gradcheck(lambda a, b: fn(a, b, merge, "geodesic", save_indices=save), (x, w), eps=1e-6, atol=1e-5)
+
+
+@pytest.mark.parametrize("merge", ["sum", "mean", "max", "min", "identity"])
+@pytest.mark.parametrize("alpha0", [-10.0, -1.0, -0.1, 0.0, 0.5, 1.0, 10.0])
+def test_gradcheck_smorph(F, merge, alpha0):
+    torch.manual_seed(1)
+    c = 2
+    x = torch.randn(1, c, 5, 6, dtype=torch.float64, device="cuda", requires_grad=True)
+    w = torch.randn(c if merge == "identity" else 3, 1 if merge == "identity" else c, 4, 3, dtype=torch.float64, device="cuda", requires_grad=True)
+    ashape = (c,) if merge == "identity" else (3, c)
+    a = (alpha0 + 0.05 * torch.randn(ashape, dtype=torch.float64, device="cuda")).requires_grad_(True)
+    assert torch.autograd.gradcheck(lambda p, q, r: F.smorph(p, q, r, channel_merge_mode=merge), (x, w, a), eps=1e-6, atol=1e-5)
+    scalar = torch.tensor([alpha0], dtype=torch.float64, device="cuda", requires_grad=True)
+    if merge != "identity":
+        assert torch.autograd.gradcheck(lambda p, q, r: F.smorph(p, q, r, channel_merge_mode=merge), (x, w, scalar), eps=1e-6, atol=1e-5)
+
+
+def test_lower_dimensional_inputs(F):
+    x2 = torch.randn(9, 8, device="cuda", requires_grad=True)
+    w2 = torch.randn(3, 3, device="cuda", requires_grad=True)
+    y = F.dilation(x2, w2, "max", "geodesic")
+    assert y.shape == (9, 8)
+    y.sum().backward()
+    assert x2.grad.shape == (9, 8) and w2.grad.shape == (3, 3)
+    x3 = torch.randn(2, 9, 8, device="cuda")
+    assert F.erosion(x3, torch.randn(4, 2, 3, 3, device="cuda")).shape == (4, 9, 8)
+    ref = F.dilation(x2.detach()[None, None], w2.detach()[None, None], "max", "geodesic")[0, 0]
+    assert torch.equal(ref, y.detach())
+
+
+def test_padding_identities(F):
+    """zero == constant(0); geodesic never wins; the interior does not depend on the padding mode
+    (the reference's tests/functional/test_padding.py:95-143)."""
+    torch.manual_seed(2)
+    x = torch.randn(1, 1, 12, 12, device="cuda")
+    w = torch.randn(1, 1, 5, 5, device="cuda")
+    for fn in (F.dilation, F.erosion):
+        outs = {p: fn(x, w, "max", p, padding_value=v) for p, v in (("zero", 0.0), ("geodesic", 0.0), ("replicate", 0.0))}
+        const0 = fn(x, w, "max", "constant", padding_value=0.0)
+        assert torch.equal(outs["zero"], const0)
+        for o in outs.values():
+            assert torch.equal(o[..., 2:-2, 2:-2], const0[..., 2:-2, 2:-2])
+        assert torch.isfinite(outs["geodesic"]).all()
+    big = F.dilation(x, w, "max", "constant", padding_value=1e6)
+    assert (big[..., 0, :] > 1e5).all()
+
+
+def test_errors(F):
+    x = torch.randn(1, 3, 8, 8, device="cuda")
+    with pytest.raises(RuntimeError, match="Input channels must match"):
+        F.dilation(x, torch.randn(2, 4, 3, 3, device="cuda"))
+    with pytest.raises(RuntimeError, match="Identity mode requires weight.shape\\[1\\] == 1"):
+        F.dilation(x, torch.randn(3, 3, 3, 3, device="cuda"), "identity")
+    with pytest.raises(RuntimeError, match="Alpha must have one value"):
+        F.smorph(x, torch.randn(2, 3, 3, 3, device="cuda"), torch.zeros(2, device="cuda"))
+    with pytest.raises(RuntimeError, match="noise_scale"):
+        F.dilation(x, torch.randn(2, 3, 3, 3, device="cuda"), noise_scale=-1.0, training=True)
+    with pytest.raises(ValueError, match="Unknown padding mode"):
+        F.dilation(x, torch.randn(2, 3, 3, 3, device="cuda"), padding_mode="nope")
+    y = F.dilation(torch.randn(1, 1, 3, 3, device="cuda"), torch.randn(1, 1, 9, 9, device="cuda"))  # SE larger than the image
+    assert y.shape == (1, 1, 3, 3) and torch.isfinite(y).all()
+
+
+def test_noise_and_dropout_paths(F):
+    """Per-sample noisy weights equal running each batch element alone with the same draw; dropout only
+    in training (the reference's tests/functional/test_weight_noise.py:42-75)."""
+    torch.manual_seed(5)
+    x = torch.randn(3, 2, 10, 11, device="cuda")
+    w = torch.randn(4, 2, 3, 3, device="cuda")
+    torch.manual_seed(123)
+    y = F.dilation(x, w, "sum", training=True, noise_scale=0.3)
+    torch.manual_seed(123)
+    noise = (torch.rand(3, 4, 2, 3, 3, device="cuda") * 2.0 - 1.0) * 0.3
+    for b in range(3):
+        assert torch.equal(y[b:b + 1], F.dilation(x[b:b + 1], w + noise[b], "sum"))
+    assert torch.equal(F.dilation(x, w, "sum", training=False, noise_scale=0.3), F.dilation(x, w, "sum"))
+    assert torch.equal(F.dilation(x, w, "max", weight_dropout=0.5, training=False), F.dilation(x, w, "max"))
+    assert torch.isfinite(F.dilation(x, w, "max", weight_dropout=0.5, training=True)).all()
+
+
+def build_cfg5(device="cuda"):
+    import morphocore_b200.nn as Mnn
+    layers = []
+    for n, (kind, ci, co, k, merge, a0) in enumerate(WL.CFG5_LAYERS):
+        if kind == "dilation":
+            layers.append(Mnn.Dilation(ci, co, k, merge))
+        elif kind == "erosion":
+            layers.append(Mnn.Erosion(ci, co, k, merge))
+        else:
+            layers.append(Mnn.SMorph(ci, co, k, merge, init_alpha=a0))
+    model = torch.nn.Sequential(*layers).to(device)
+    with torch.no_grad():
+        for layer, w in zip(model, WL.cfg5_weights()):
+            layer.weight.copy_(w)
+    return model
+
+
+def test_cfg5_training_step_matches_reference(golden):
+    """The 4-layer stack at B = 2: loss, sampled outputs and every parameter gradient against the
+    reference's (fp32: rtol 1e-3 on gradients that are sums of ~6e6 terms, atol scaled)."""
+    data = golden("full_size")
+    model = build_cfg5()
+    x, target = WL.cfg5_batch(B=256, start=0, count=2)
+    out = model(x.cuda())
+    loss = torch.nn.functional.mse_loss(out, target.cuda())
+    loss.backward()
+    assert abs(loss.item() - data["cfg5_loss"][0]) < 1e-4 * abs(data["cfg5_loss"][0])
+    pos = torch.from_numpy(data["cfg5_out_pos"]).cuda()
+    np.testing.assert_allclose(out.detach().reshape(-1)[pos].cpu().numpy(), data["cfg5_out_val"], rtol=1e-4, atol=1e-4)
+    for n, layer in enumerate(model):
+        want = data[f"cfg5_gw{n}"]
+        np.testing.assert_allclose(layer.weight.grad.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * float(np.abs(want).max()))
+        if hasattr(layer, "alpha"):
+            want = data[f"cfg5_galpha{n}"]
+            np.testing.assert_allclose(layer.alpha.grad.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * float(np.abs(want).max()))

@@ -1,0 +1,292 @@
+"""Parity of the CUDA kernels, called through the C-ABI, with the golden fixtures (outputs of the
+reference's own CPU code) and with the C oracle on seeded inputs.
+
+Bars: dilation / erosion forward is BIT-EXACT (values compared with array_equal) for every merge,
+padding and dtype, and so are the packed winner indices; gradients and smorph are compared within the
+tolerances stated beside each assertion (summation order differs from the reference, whose own weight
+gradient is not reproducible run to run)."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+import workloads as WL
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+MERGES = ("max", "min", "sum", "mean", "identity")
+
+
+@pytest.fixture(scope="module")
+def C():
+    import _cabi
+    return _cabi
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def flip(w):
+    return np.ascontiguousarray(w[..., ::-1, ::-1])
+
+
+def grad_tol(dtype, scale=1.0):
+    # fp32: the reference's own CPU<->CUDA bar (rtol 1e-4), atol scaled to the magnitude of the sums
+    return dict(rtol=1e-4, atol=1e-5 * scale) if dtype == np.float32 else dict(rtol=1e-11, atol=1e-12 * scale)
+
+
+def test_morph_golden_fixtures(C, manifest, golden):
+    data = golden("morph_small")
+    for case in manifest["morph_small"]:
+        k = case["key"]
+        x, w, gy = data[k + "_x"], data[k + "_w"], data[k + "_gy"]
+        op, merge, padding, pv = case["op"], case["merge"], case["padding"], case["padding_value"]
+        wk = w if op == "dilation" else flip(w)
+        y = C.morpho_forward(op, dev(x), dev(wk), merge, padding, pv)
+        assert np.array_equal(y.cpu().numpy(), data[k + "_y"]), f"forward not bit-exact: {case}"
+        gx, gw = C.morpho_backward(op, dev(x), dev(wk), dev(gy), merge, padding, pv)
+        gw = gw.cpu().numpy()
+        if op == "erosion":
+            gw = flip(gw)
+        tol = grad_tol(x.dtype, scale=float(np.abs(gy).sum()) / 100)
+        np.testing.assert_allclose(gx.cpu().numpy(), data[k + "_gx"], **grad_tol(x.dtype), err_msg=str(case))
+        np.testing.assert_allclose(gw, data[k + "_gw"], **tol, err_msg=str(case))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("op", ["dilation", "erosion"])
+def test_morph_exhaustive_small_shapes(C, op, dtype):
+    """Every H, W in 1..6 (plus sizes around the 64 x 32 tile), k in {1, 2, 3, 4, 5}, all merges, two paddings,
+    against the oracle: forward bit-exact, winner indices identical."""
+    rng = np.random.default_rng(5)
+    shapes = [(h, w) for h in range(1, 7) for w in range(1, 7)] + [(31, 63), (32, 64), (33, 65), (40, 130)]
+    for (H, W) in shapes:
+        for (kH, kW) in ((1, 1), (3, 3), (2, 3), (5, 5), (4, 1)) if H <= 6 else ((3, 3), (5, 4), (7, 7)):
+            for merge in MERGES:
+                Ci, Co = (3, 3) if merge == "identity" else (2, 5)
+                x = rng.integers(-3, 4, (2, Ci, H, W)).astype(dtype) if (H + W) % 2 else rng.standard_normal((2, Ci, H, W)).astype(dtype)
+                w = rng.standard_normal((Co, 1 if merge == "identity" else Ci, kH, kW)).astype(dtype).round(1)
+                for padding, pv in (("replicate", 0.0), ("constant", 0.5), ("geodesic", 0.0)):
+                    want, want_idx = O.morpho_forward(op, x, w, merge, padding, pv, with_index=True)
+                    got, got_idx = C.morpho_forward(op, dev(x), dev(w), merge, padding, pv, with_index=True)
+                    assert np.array_equal(got.cpu().numpy(), want), (op, merge, padding, H, W, kH, kW)
+                    if merge in ("max", "min"):
+                        assert np.array_equal(got_idx.cpu().numpy(), want_idx), (op, merge, padding, H, W, kH, kW)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("k", [3, 5, 7, 11, (9, 9), (6, 3)])
+def test_morph_kernel_sizes_forward_and_backward(C, k, dtype):
+    """Specialised widths (3, 5, 7, 11) and the any-size path, larger channel counts, against the oracle."""
+    rng = np.random.default_rng(11)
+    kH, kW = (k, k) if isinstance(k, int) else k
+    for op in ("dilation", "erosion"):
+        for merge in MERGES:
+            Ci, Co = (6, 6) if merge == "identity" else (5, 7)
+            x = rng.standard_normal((2, Ci, 37, 70)).astype(dtype)
+            w = (0.3 * rng.standard_normal((Co, 1 if merge == "identity" else Ci, kH, kW))).astype(dtype)
+            gy = rng.standard_normal((2, Co, 37, 70)).astype(dtype)
+            for padding in ("replicate", "zero"):
+                want = O.morpho_forward(op, x, w, merge, padding)
+                got = C.morpho_forward(op, dev(x), dev(w), merge, padding)
+                assert np.array_equal(got.cpu().numpy(), want), (op, merge, padding, k)
+                wgx, wgw = O.morpho_backward(op, x, w, gy, merge, padding)
+                gx, gw = C.morpho_backward(op, dev(x), dev(w), dev(gy), merge, padding)
+                np.testing.assert_allclose(gx.cpu().numpy(), wgx, **grad_tol(dtype, 10), err_msg=str((op, merge, padding, k)))
+                np.testing.assert_allclose(gw.cpu().numpy(), wgw, **grad_tol(dtype, 100), err_msg=str((op, merge, padding, k)))
+
+
+def test_saved_indices_equal_recomputed(C):
+    """MAX / MIN backward from the saved winners equals the backward that recomputes them into the
+    workspace (the reference's save_indices=True / False equivalence)."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((3, 4, 45, 83)).astype(np.float32)
+    w = rng.standard_normal((6, 4, 5, 5)).astype(np.float32)
+    gy = rng.standard_normal((3, 6, 45, 83)).astype(np.float32)
+    for op in ("dilation", "erosion"):
+        for merge in ("max", "min"):
+            y, idx = C.morpho_forward(op, dev(x), dev(w), merge, "replicate", with_index=True)
+            _, want_idx = O.morpho_forward(op, x, w, merge, "replicate", with_index=True)
+            assert np.array_equal(idx.cpu().numpy(), want_idx)
+            a = C.morpho_backward(op, dev(x), dev(w), dev(gy), merge, "replicate", idx=idx)
+            b = C.morpho_backward(op, dev(x), dev(w), dev(gy), merge, "replicate", idx=None)
+            np.testing.assert_allclose(a[0].cpu().numpy(), b[0].cpu().numpy(), rtol=1e-5, atol=1e-5)
+            np.testing.assert_allclose(a[1].cpu().numpy(), b[1].cpu().numpy(), rtol=1e-4, atol=1e-3)
+            wgx, wgw = O.morpho_backward(op, x, w, gy, merge, "replicate")
+            np.testing.assert_allclose(a[0].cpu().numpy(), wgx, rtol=1e-4, atol=1e-5)
+            np.testing.assert_allclose(a[1].cpu().numpy(), wgw, rtol=1e-4, atol=1e-3)
+
+
+def test_ties_route_to_first_tap_and_channel_zero(C):
+    """All-equal input: tap (0, 0) and channel 0 take every gradient; with replicate padding grad_weight
+    receives all 25 contributions of a 5 x 5 image but grad_input only those whose tap (0, 0) is inside."""
+    x = torch.zeros(1, 2, 5, 5, device="cuda")
+    w = torch.zeros(1, 2, 3, 3, device="cuda")
+    gy = torch.ones(1, 1, 5, 5, device="cuda")
+    gx, gw = C.morpho_backward("dilation", x, w, gy, "max", "replicate")
+    assert gw[0, 0, 0, 0].item() == 25 and gw.sum().item() == 25
+    assert gx[0, 0].sum().item() == 16 and gx[0, 1].abs().sum().item() == 0
+    gx, gw = C.morpho_backward("erosion", x, w, gy, "sum", "zero")
+    assert gw[0, :, 0, 0].tolist() == [-25.0, -25.0] and gx.sum().item() == 32
+
+
+def test_per_sample_weights(C):
+    """weight_batch_stride: one structuring element per batch element equals running each element alone,
+    and grad_weight is the sum over the batch."""
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((3, 2, 20, 33)).astype(np.float32)
+    w5 = rng.standard_normal((3, 4, 2, 3, 3)).astype(np.float32)
+    gy = rng.standard_normal((3, 4, 20, 33)).astype(np.float32)
+    for merge in ("sum", "max"):
+        y = C.morpho_forward("dilation", dev(x), dev(w5), merge)
+        gx, gw = C.morpho_backward("dilation", dev(x), dev(w5), dev(gy), merge)
+        gw_sum = np.zeros((4, 2, 3, 3), np.float32)
+        for b in range(3):
+            yb = O.morpho_forward("dilation", x[b:b + 1], w5[b], merge)
+            assert np.array_equal(y[b:b + 1].cpu().numpy(), yb)
+            gxb, gwb = O.morpho_backward("dilation", x[b:b + 1], w5[b], gy[b:b + 1], merge)
+            np.testing.assert_allclose(gx[b:b + 1].cpu().numpy(), gxb, rtol=1e-4, atol=1e-5)
+            gw_sum += gwb
+        np.testing.assert_allclose(gw.cpu().numpy(), gw_sum, rtol=1e-4, atol=1e-3)
+
+
+def smorph_tols(dtype, alpha0):
+    big = abs(alpha0) >= 100
+    if dtype == np.float32:
+        # rtol 1e-4 / atol 1e-5 (the stated fp32 bar); gradients multiply exp rounding by alpha
+        return dict(rtol=1e-4, atol=1e-5), dict(rtol=1e-4 * (100 if big else 1), atol=1e-5 * (1000 if big else 3))
+    return dict(rtol=1e-10, atol=1e-11), dict(rtol=1e-10 * (100 if big else 1), atol=1e-11 * (1000 if big else 1))
+
+
+def test_smorph_golden_fixtures(C, manifest, golden):
+    data = golden("smorph_small")
+    for case in manifest["smorph_small"]:
+        k = case["key"]
+        x, w, alpha, gy = data[k + "_x"], data[k + "_w"], data[k + "_alpha"], data[k + "_gy"]
+        merge = case["merge"]
+        wt = O.smorph_weight(w, alpha, merge)
+        ytol, gtol = smorph_tols(x.dtype, case["alpha0"])
+        y = C.smorph_forward(dev(x), dev(wt), dev(alpha), merge)
+        np.testing.assert_allclose(y.cpu().numpy(), data[k + "_y"], **ytol, err_msg=str(case))
+        gx, gwt, ga = C.smorph_backward(dev(x), dev(wt), dev(alpha), y, dev(gy), merge)
+        np.testing.assert_allclose(gx.cpu().numpy(), data[k + "_gx"], **gtol, err_msg=str(case))
+        # operator-level gradients of w~ and alpha against the oracle (the fixture holds the gradients of
+        # the user-level w and alpha, checked through autograd in test_gpu_autograd.py)
+        ogx, ogw, oga = O.smorph_backward(x, wt, alpha, gy, merge)
+        wtol = dict(rtol=gtol["rtol"], atol=gtol["atol"] * 30)
+        np.testing.assert_allclose(gwt.cpu().numpy(), ogw, **wtol, err_msg=str(case))
+        np.testing.assert_allclose(ga.cpu().numpy().reshape(-1), oga.reshape(-1), **wtol, err_msg=str(case))
+
+
+def mask_ambiguous_winners(gy, x, w, alpha, merge):
+    """MAX / MIN merges share the gradient between the channels whose soft extremum lies within 1e-6 of
+    the merged value: a step function of the channel outputs. Where the runner-up is closer than 1e-5
+    the last bits of exp() decide which side of the step a pixel falls on, in the reference as well, so
+    those pixels get a zero output gradient in the comparison."""
+    if merge not in ("max", "min"):
+        return gy
+    Ci = x.shape[1]
+    outs = np.stack([O.smorph_forward(x[:, i:i + 1], w[:, i:i + 1], alpha[:, i:i + 1], "sum") for i in range(Ci)], 0)
+    srt = np.sort(outs, 0)
+    gap = (srt[1] - srt[0]) if merge == "min" else (srt[-1] - srt[-2])
+    gy = gy.copy()
+    gy[gap < 1e-5] = 0
+    return gy
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("k", [3, 5, 7, (4, 3), 11])
+def test_smorph_against_oracle(C, k, dtype):
+    rng = np.random.default_rng(21)
+    kH, kW = (k, k) if isinstance(k, int) else k
+    for merge in MERGES:
+        Ci, Co = (4, 4) if merge == "identity" else (3, 5)
+        x = rng.standard_normal((2, Ci, 35, 67)).astype(dtype)
+        w = (0.2 * rng.standard_normal((Co, 1 if merge == "identity" else Ci, kH, kW))).astype(dtype)
+        gy = rng.standard_normal((2, Co, 35, 67)).astype(dtype)
+        for a0 in (-8.0, -1.0, 0.0, 2.0, 30.0):
+            ashape = (Co,) if merge == "identity" else (Co, Ci)
+            alpha = (a0 + 0.1 * rng.standard_normal(ashape)).astype(dtype)
+            if a0 == 0.0:
+                alpha[...] = 0.0
+            ytol, gtol = smorph_tols(dtype, a0)
+            want = O.smorph_forward(x, w, alpha, merge)
+            y = C.smorph_forward(dev(x), dev(w), dev(alpha), merge)
+            np.testing.assert_allclose(y.cpu().numpy(), want, **ytol, err_msg=str((merge, k, a0)))
+            g = mask_ambiguous_winners(gy, x, w, alpha, merge)
+            wgx, wgw, wga = O.smorph_backward(x, w, alpha, g, merge)
+            gx, gw, ga = C.smorph_backward(dev(x), dev(w), dev(alpha), y, dev(g), merge)
+            np.testing.assert_allclose(gx.cpu().numpy(), wgx, **gtol, err_msg=str((merge, k, a0)))
+            sums = dict(rtol=gtol["rtol"], atol=gtol["atol"] * 100)
+            np.testing.assert_allclose(gw.cpu().numpy(), wgw, **sums, err_msg=str((merge, k, a0)))
+            np.testing.assert_allclose(ga.cpu().numpy().reshape(-1), wga.reshape(-1), **sums, err_msg=str((merge, k, a0)))
+
+
+def sha(t):
+    return hashlib.sha256(t.cpu().numpy().tobytes()).hexdigest()
+
+
+def entry(manifest, key):
+    return next(m for m in manifest["full_size"] if m["key"] == key)
+
+
+def test_cfg1_full_size_bit_exact(C, manifest):
+    c = WL.cfg1()
+    y = C.morpho_forward("dilation", c["x"].cuda(), c["w"].cuda(), "max", "replicate")
+    assert sha(y) == entry(manifest, "cfg1")["y_sha256"]
+
+
+def test_cfg2_full_size(C, manifest, golden):
+    """Config 2 at full size: forward SHA-256 equals the reference's; grad_weight and sampled grad_input
+    within rtol 1e-4 (atol scaled to the sums)."""
+    data = golden("full_size")
+    c = WL.cfg2()
+    x, wk, gy = c["x"].cuda(), c["w"].flip((-2, -1)).contiguous().cuda(), c["gy"].cuda()
+    y = C.morpho_forward("erosion", x, wk, "sum", "replicate")
+    assert sha(y) == entry(manifest, "cfg2")["y_sha256"]
+    gx, gw = C.morpho_backward("erosion", x, wk, gy, "sum", "replicate")
+    gw = gw.flip((-2, -1)).cpu().numpy()
+    np.testing.assert_allclose(gw, data["cfg2_gw"], rtol=1e-4, atol=0.05)
+    np.testing.assert_allclose(gx.reshape(-1)[torch.from_numpy(data["cfg2_gx_pos"]).cuda()].cpu().numpy(), data["cfg2_gx_val"], rtol=1e-4, atol=1e-4)
+    # size-independent property: every output pixel sends its gradient to exactly one tap per pair
+    assert abs(gw.sum() / (-16 * c["gy"].double().sum().item()) - 1) < 1e-3
+
+
+@pytest.mark.parametrize("alpha", WL.CFG3_ALPHAS)
+def test_cfg3_full_size(C, golden, alpha):
+    data = golden("full_size")
+    key = f"cfg3_a{alpha:g}"
+    c = WL.cfg3(alpha)
+    wt = torch.from_numpy(O.smorph_weight(c["w"].numpy(), c["alpha"].numpy(), "mean")).cuda()
+    x, a, gy = c["x"].cuda(), c["alpha"].cuda(), c["gy"].cuda()
+    y = C.smorph_forward(x, wt, a, "mean")
+    pos = torch.from_numpy(data[key + "_pos"]).cuda()
+    np.testing.assert_allclose(y.reshape(-1)[pos].cpu().numpy(), data[key + "_y_val"], rtol=1e-4, atol=1e-5)
+    gx, gwt, ga = C.smorph_backward(x, wt, a, y, gy, "mean")
+    np.testing.assert_allclose(gx.reshape(-1)[pos].cpu().numpy(), data[key + "_gx_val"], rtol=1e-4, atol=1e-5)
+    assert torch.isfinite(gwt).all() and torch.isfinite(ga).all()
+
+
+@pytest.mark.parametrize("op", ["dilation", "erosion"])
+def test_cfg4_full_size_bit_exact(C, manifest, golden, op):
+    data = golden("full_size")
+    c = WL.cfg4(op)
+    w = c["w"] if op == "dilation" else c["w"].flip((-2, -1)).contiguous()
+    y = C.morpho_forward(op, c["x"].cuda(), w.cuda(), "identity", "replicate")
+    assert sha(y) == entry(manifest, f"cfg4_{op}")["y_sha256"]
+    del y
+    c = WL.cfg4(op, B=2, C=8, HW=256)
+    w = c["w"] if op == "dilation" else c["w"].flip((-2, -1)).contiguous()
+    x, w, gy = c["x"].cuda(), w.cuda(), c["gy"].cuda()
+    y = C.morpho_forward(op, x, w, "identity", "replicate")
+    assert sha(y) == entry(manifest, f"cfg4s_{op}")["y_sha256"]
+    gx, gw = C.morpho_backward(op, x, w, gy, "identity", "replicate")
+    if op == "erosion":
+        gw = gw.flip((-2, -1))
+    # fp64: 1e-12 relative to the magnitude of the sums
+    np.testing.assert_allclose(gw.cpu().numpy(), data[f"cfg4s_{op}_gw"], rtol=1e-12, atol=1e-12 * float(c["gy"].abs().sum()))
+    np.testing.assert_allclose(gx.reshape(-1)[torch.from_numpy(data[f"cfg4s_{op}_gx_pos"]).cuda()].cpu().numpy(),
+                               data[f"cfg4s_{op}_gx_val"], rtol=1e-12, atol=1e-12)
