@@ -80,6 +80,21 @@ size_t mc_morpho_backward_workspace_bytes(const mc_desc* desc, int have_idx);
 int mc_morpho_backward(const mc_desc* desc, const void* x, const void* w, const int32_t* idx, const void* gy, void* gx, void* gw,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Backward dilation / erosion for hosts that cannot allocate device memory (a server whose arena owns the
+ * whole GPU, a plugin inside another framework's pool, a loop that cannot afford cudaMalloc's device
+ * synchronisation). Same results as mc_morpho_backward called with idx = NULL, but the winners of MAX /
+ * MIN merges are recomputed into a fixed MC_NOALLOC_SCRATCH_BYTES array inside the library image instead
+ * of a caller workspace: no allocation by either side. This entry point has no counterpart in the
+ * reference, whose wrapper always allocates with torch.
+ *  - limit: B*Co*H*W <= MC_NOALLOC_SCRATCH_BYTES / 4 output pixels for MAX / MIN merges (other merges need
+ *    no scratch and have no limit); larger calls return MC_ERR_UNSUPPORTED;
+ *  - every GPU that loads the library holds the array until the process exits;
+ *  - the first call on each device resolves the array's address: make it before any stream capture;
+ *  - calls on one device share the array (it keeps the last call's winners; nothing needs zeroing, each
+ *    call overwrites what it reads), so calls that overlap on the GPU race: serialise them. */
+#define MC_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u)
+int mc_morpho_backward_noalloc(const mc_desc* desc, const void* x, const void* w, const void* gy, void* gx, void* gw, void* stream);
+
 /* Forward smorph (alpha-softmax soft extremum) with the fused channel merge.
  * Replaces smorph_forward_cuda<T> (CU/smorph.cuh:15-18, CU/smorph.cu:52-61) for every merge but SMOOTH.
  * alpha_pairs holds one value per (o, i) pair, [Co, Ci] ([Co] for identity), as produced by
