@@ -1,9 +1,11 @@
 // Shared device / host helpers of the sm_100a morphology kernels.
 //
 // Tiling used by every tile kernel in this folder: a CTA of 256 threads owns a 64 x 32 tile of output
-// pixels of one image plane; thread (tx, ty) = (tid % 16, tid / 16) owns the 4 x 2 pixel patch at
-// columns 4 tx .. 4 tx + 3 and rows 2 ty, 2 ty + 1, so its window rows are read from shared memory
-// with conflict-free 128-bit loads. The shared window of a tile holds the tile plus the halo of the
+// pixels of one image plane; thread (tx, ty) owns the 4 x 2 pixel patch at columns 4 tx .. 4 tx + 3 and
+// rows 2 ty, 2 ty + 1. A warp is 8 threads wide and 4 tall, a 32 x 8 pixel block of the tile (see
+// thread_patch): its 128-bit shared loads are conflict free (8 lanes = 128 contiguous bytes of one window
+// row), and a warp whose block lies entirely outside the image (partial tiles of a 224-wide image) skips
+// its arithmetic. The shared window of a tile holds the tile plus the halo of the
 // structuring element with the border already resolved:
 //     window row r    <-> image row  tile_h0 - (kH - 1 - kH/2) + r
 //     window column c <-> image col  tile_w0 - (kW - 1 - kW/2) + c
@@ -74,16 +76,31 @@ inline Geometry make_geometry(const mc_desc& d, int elem_bytes)
     return g;
 }
 
+/// Patch coordinates of the calling thread and whether its warp's 32 x 8 pixel block has any pixel
+/// inside the image.
+__device__ __forceinline__ void thread_patch(int tile_h0, int tile_w0, int H, int W, int& tx, int& ty, bool& warp_live)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    tx = (lane & 7) + 8 * (warp & 1);
+    ty = (lane >> 3) + 4 * (warp >> 1);
+    warp_live = tile_w0 + 32 * (warp & 1) < W && tile_h0 + 8 * (warp >> 1) < H;
+}
+
 template <typename T> struct Limits;
 template <> struct Limits<float>
 {
     __host__ __device__ static constexpr float inf() { return __builtin_huge_valf(); }
     __host__ __device__ static constexpr float max() { return 3.402823466e+38f; }
+    // "Never wins, never overflows": sums of a few hundred of these stay finite.
+    __host__ __device__ static constexpr float big() { return 1e30f; }
+    __host__ __device__ static constexpr float tiny() { return 1e-20f; }
 };
 template <> struct Limits<double>
 {
     __host__ __device__ static constexpr double inf() { return __builtin_huge_val(); }
     __host__ __device__ static constexpr double max() { return 1.7976931348623157e+308; }
+    __host__ __device__ static constexpr double big() { return 1e300; }
+    __host__ __device__ static constexpr double tiny() { return 1e-200; }
 };
 
 /// Stage the window of one image plane into shared memory, border resolved: REPLICATE clamps to the edge
@@ -110,6 +127,31 @@ __device__ __forceinline__ void load_window(T* __restrict__ dst, const T* __rest
             T v = outside;
             if (in || g.replicate) v = __ldg(src + min(max(ix, 0), g.W - 1));
             out[c] = v;
+        }
+    }
+}
+
+/// Stage the window of one plane for the smorph kernels, whose taps outside the image are excluded: `pos`
+/// receives x and `neg` receives -x (either may be null), and both read -big outside the image, a value
+/// that never wins a maximum and whose exponential is exactly zero.
+template <typename T>
+__device__ __forceinline__ void load_window_signed(T* __restrict__ pos, T* __restrict__ neg, const T* __restrict__ plane, const Geometry& g,
+                                                   int tile_h0, int tile_w0)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
+    for (int r = warp; r < g.win_rows; r += THREADS / 32)
+    {
+        const int iy = row0 + r;
+        const bool row_in = iy >= 0 && iy < g.H;
+        const T* src = plane + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W;
+        for (int c = lane; c < g.win_stride; c += 32)
+        {
+            const int ix = col0 + c;
+            const bool in = row_in && ix >= 0 && ix < g.W;
+            const T v = in ? __ldg(src + ix) : T(0);
+            if (pos != nullptr) pos[r * g.win_stride + c] = in ? v : -Limits<T>::big();
+            if (neg != nullptr) neg[r * g.win_stride + c] = in ? -v : -Limits<T>::big();
         }
     }
 }

@@ -150,7 +150,10 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
     const int tile = (blockIdx.x / g.Ci) % tiles;
     const int b = blockIdx.x / (g.Ci * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    const int tx = threadIdx.x % (TILE_W / PATCH_W), ty = threadIdx.x / (TILE_W / PATCH_W);
+    int tx, ty;
+    bool warp_live;
+    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);  // threads of dead warps load zero gradients and skip below
+    (void)warp_live;
     const int64_t plane = g.plane();
     const T* wb = a.w + static_cast<int64_t>(b) * g.weight_batch_stride;
     const int wci = g.identity ? 1 : g.Ci;

@@ -147,7 +147,9 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
     const int tile = (blockIdx.x / a.o_groups) % tiles;
     const int b = blockIdx.x / (a.o_groups * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    const int tx = threadIdx.x % (TILE_W / PATCH_W), ty = threadIdx.x / (TILE_W / PATCH_W);
+    int tx, ty;
+    bool warp_live;
+    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
     const int o0 = og * OB;
     const int64_t plane = g.plane();
     const T* xb = a.x + static_cast<int64_t>(b) * g.Ci * plane;
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
         stage_weights<T, IS_MIN, OB>(sw, wb, g, o0, c0, cc);
         __syncthreads();
 
-        for (int c = 0; c < cc; c++)
+        for (int c = 0; c < cc && warp_live; c++)
         {
             T acc[OB][PATCH_H][PATCH_W];
 #pragma unroll

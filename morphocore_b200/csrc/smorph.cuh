@@ -6,10 +6,11 @@
 //     e_k = exp(alpha (v_k - ref)),  S = sum e_k,  out = (sum e_k v_k) / S
 // (reference: morphocore/functional/csrc/cpp/smorph_cpu_kernels.hxx:14-24, 76-147; CUDA kernels
 // csrc/cuda/smorph_kernels.cuh:80-175, 307-407, 418-571). The kernels work on u = s v with s = sign(alpha),
-// so both cases are a max: u_k = s x_k + (s w_k) is one fused multiply-add with the sign folded into
-// the staged structuring element, and alpha (v_k - ref) = |alpha| (u_k - ref_u) <= 0.
-// Out-of-image window elements are staged as NaN: max ignores them in the first pass, and the second
-// pass turns them into e = 0.
+// so both cases are a max and alpha (v_k - ref) = |alpha| (u_k - ref_u) <= 0: a pair with alpha >= 0 reads the
+// window of x and the structuring element w, a pair with alpha < 0 the window of -x and -w, and
+// u_k = xs_k + ws_k is one add. Window elements outside the image hold -1e30 in both windows: they never
+// win the maximum and their exponential is exactly zero (the exponent scale is clamped to 1e-20 from
+// below so that this also holds for alpha = 0), so excluded taps cost no instruction.
 #pragma once
 #include "common.cuh"
 #include "morpho_backward.cuh"
@@ -23,38 +24,52 @@ constexpr float LOG2E_F = 1.4426950408889634f;
 /// scale pre-multiplied by log2(e); double uses exp().
 __device__ __forceinline__ float soft_exp(float d, float scale2)
 {
-    float t = d * scale2, e;
-    t = fmaxf(t, -Limits<float>::inf());  // NaN (excluded tap) -> -inf -> e = 0
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(d * scale2));
     return e;
 }
-__device__ __forceinline__ double soft_exp(double d, double scale)
-{
-    const double t = fmax(d * scale, -Limits<double>::inf());
-    return exp(t);
-}
-__device__ __forceinline__ float exp_scale(float abs_alpha) { return abs_alpha * LOG2E_F; }
-__device__ __forceinline__ double exp_scale(double abs_alpha) { return abs_alpha; }
+__device__ __forceinline__ double soft_exp(double d, double scale) { return exp(d * scale); }
+__device__ __forceinline__ float exp_scale(float abs_alpha) { return fmaxf(abs_alpha * LOG2E_F, Limits<float>::tiny()); }
+__device__ __forceinline__ double exp_scale(double abs_alpha) { return fmax(abs_alpha, Limits<double>::tiny()); }
 
-/// Visit every tap of the thread's 2 x 4 patch: f(k, rr, j, x) with k = kh * kW + kw.
-template <int KW, typename T, typename F>
+/// 1 / x for x >= 1 (a sum of exponentials whose largest term is 1); float: hardware reciprocal, 1 ulp.
+__device__ __forceinline__ float soft_rcp(float x)
+{
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ double soft_rcp(double x) { return 1.0 / x; }
+
+/// Visit every tap of the thread's 2 x 4 patch: f(kh, kw, rr, j, x). KW > 0 reads whole row segments with
+/// 128-bit loads and unrolls the kernel row; KH > 0 also unrolls the kernel rows, so that every index the
+/// callback receives is a compile-time constant.
+template <int KH, int KW, typename T, typename F>
 __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Geometry& g, int tx, int ty, F f)
 {
     if constexpr (KW > 0)
     {
         constexpr int LEN = segment_len(KW, sizeof(T));
-        for (int kh = 0; kh < g.kH; kh++)
-        {
+        auto row = [&](int kh, int top) {
             T seg[PATCH_H][LEN];
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++)
-                load_segment<LEN>(seg[rr], win + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W);
+                load_segment<LEN>(seg[rr], win + (ty * PATCH_H + rr + top - kh) * g.win_stride + tx * PATCH_W);
 #pragma unroll
             for (int kw = 0; kw < KW; kw++)
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++) f(kh * KW + kw, rr, j, seg[rr][j + KW - 1 - kw]);
+                    for (int j = 0; j < PATCH_W; j++) f(kh, kw, rr, j, seg[rr][j + KW - 1 - kw]);
+        };
+        if constexpr (KH > 0)
+        {
+#pragma unroll
+            for (int kh = 0; kh < KH; kh++) row(kh, KH - 1);
+        }
+        else
+        {
+            for (int kh = 0; kh < g.kH; kh++) row(kh, g.kH - 1);
         }
     }
     else
@@ -66,23 +81,27 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++) f(kh * g.kW + kw, rr, j, row0[rr * g.win_stride + j + g.kW - 1 - kw]);
+                    for (int j = 0; j < PATCH_W; j++) f(kh, kw, rr, j, row0[rr * g.win_stride + j + g.kW - 1 - kw]);
         }
     }
 }
 
-/// Soft extremum of one staged pair for the thread's patch, in the u domain: ref_u, S and out_u.
-template <int KW, typename T>
-__device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* __restrict__ swk, int wstride, T s, T scale, const Geometry& g,
-                                            int tx, int ty, T (&ref)[PATCH_H][PATCH_W], T (&sum)[PATCH_H][PATCH_W], T (&out)[PATCH_H][PATCH_W])
+/// Soft extremum of one staged pair for the thread's patch, in the u domain: ref_u, 1 / S and out_u.
+/// `win` is the window of s x and `swk` the structuring element s w (element k at swk[k * wstride]).
+template <int KH, int KW, typename T>
+__device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* __restrict__ swk, int wstride, T scale, const Geometry& g, int tx,
+                                            int ty, T (&ref)[PATCH_H][PATCH_W], T (&inv_sum)[PATCH_H][PATCH_W], T (&out)[PATCH_H][PATCH_W])
 {
+    const int kwr = KW > 0 ? KW : g.kW;
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
         for (int j = 0; j < PATCH_W; j++) ref[rr][j] = -Limits<T>::inf();
-    for_each_tap<KW>(win, g, tx, ty, [&](int k, int rr, int j, T xv) { ref[rr][j] = ext2<false>(ref[rr][j], fma(s, xv, swk[k * wstride])); });
+    for_each_tap<KH, KW>(win, g, tx, ty, [&](int kh, int kw, int rr, int j, T xv) {
+        ref[rr][j] = ext2<false>(ref[rr][j], xv + swk[(kh * kwr + kw) * wstride]);
+    });
 
-    T weighted[PATCH_H][PATCH_W];
+    T sum[PATCH_H][PATCH_W], weighted[PATCH_H][PATCH_W];
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -91,17 +110,20 @@ __device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* 
             sum[rr][j] = T(0);
             weighted[rr][j] = T(0);
         }
-    for_each_tap<KW>(win, g, tx, ty, [&](int k, int rr, int j, T xv) {
-        const T u = fma(s, xv, swk[k * wstride]);
+    for_each_tap<KH, KW>(win, g, tx, ty, [&](int kh, int kw, int rr, int j, T xv) {
+        const T u = xv + swk[(kh * kwr + kw) * wstride];
         const T e = soft_exp(u - ref[rr][j], scale);
-        const T us = ext2<false>(u, -Limits<T>::max());  // NaN -> finite, so that 0 * us stays 0
         sum[rr][j] += e;
-        weighted[rr][j] = fma(e, us, weighted[rr][j]);
+        weighted[rr][j] = fma(e, u, weighted[rr][j]);
     });
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-        for (int j = 0; j < PATCH_W; j++) out[rr][j] = weighted[rr][j] * (T(1) / sum[rr][j]);
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            inv_sum[rr][j] = soft_rcp(sum[rr][j]);
+            out[rr][j] = weighted[rr][j] * inv_sum[rr][j];
+        }
 }
 
 template <typename T>
@@ -128,22 +150,24 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const Geometry& g = a.g;
     const int taps = g.taps();
-    T* sx = reinterpret_cast<T*>(smem_raw);
-    T* sw = sx + a.chunk * g.window_elems();     // [chunk][taps][OB], sign folded
-    T* sa = sw + a.chunk * taps * OB;            // [chunk][OB][2]: sign, exp scale
+    const int welems = g.window_elems();
+    T* sx = reinterpret_cast<T*>(smem_raw);   // [chunk][2][window]: x and -x
+    T* sw = sx + a.chunk * 2 * welems;         // [chunk][taps][OB], sign folded
+    T* sa = sw + a.chunk * taps * OB;          // [chunk][OB][2]: sign, exp scale
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int og = blockIdx.x % a.o_groups;
     const int tile = (blockIdx.x / a.o_groups) % tiles;
     const int b = blockIdx.x / (a.o_groups * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    const int tx = threadIdx.x % (TILE_W / PATCH_W), ty = threadIdx.x / (TILE_W / PATCH_W);
+    int tx, ty;
+    bool warp_live;
+    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
     const int o0 = og * OB;
     const int64_t plane = g.plane();
     const T* xb = a.x + static_cast<int64_t>(b) * g.Ci * plane;
     const int channels = g.identity ? 1 : g.Ci;
     const int wci = g.identity ? 1 : g.Ci;
-    const T nan = __longlong_as_double(0x7ff8000000000000LL);
 
     T merged[OB][PATCH_H][PATCH_W];
     T target[OB][PATCH_H][PATCH_W];
@@ -167,11 +191,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
     {
         const int cc = min(a.chunk, channels - c0);
         __syncthreads();
-        for (int c = 0; c < cc; c++)
-        {
-            const int ci = g.identity ? o0 : c0 + c;
-            load_window(sx + c * g.window_elems(), xb + static_cast<int64_t>(ci) * plane, g, tile_h0, tile_w0, nan);
-        }
+        bool has_pos = false, has_neg = false;
         for (int e = threadIdx.x; e < cc * OB; e += THREADS)
         {
             const int o = e % OB, c = e / OB;
@@ -179,6 +199,8 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             if (o0 + o < g.Co) al = __ldg(a.alpha + (g.identity ? o0 + o : static_cast<int64_t>(o0 + o) * g.Ci + c0 + c));
             sa[e * 2] = al >= T(0) ? T(1) : T(-1);
             sa[e * 2 + 1] = exp_scale(al >= T(0) ? al : -al);
+            has_pos |= al >= T(0);
+            has_neg |= al < T(0);
         }
         for (int e = threadIdx.x; e < cc * taps * OB; e += THREADS)
         {
@@ -192,16 +214,26 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             }
             sw[e] = al >= T(0) ? v : -v;
         }
+        // Only the windows some pair of this chunk reads are staged.
+        has_pos = __syncthreads_or(has_pos);
+        has_neg = __syncthreads_or(has_neg);
+        for (int c = 0; c < cc; c++)
+        {
+            const int ci = g.identity ? o0 : c0 + c;
+            load_window_signed(has_pos ? sx + (2 * c) * welems : nullptr, has_neg ? sx + (2 * c + 1) * welems : nullptr,
+                               xb + static_cast<int64_t>(ci) * plane, g, tile_h0, tile_w0);
+        }
         __syncthreads();
 
-        for (int c = 0; c < cc; c++)
+        for (int c = 0; c < cc && warp_live; c++)
         {
 #pragma unroll
             for (int o = 0; o < OB; o++)
             {
                 const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
-                T ref[PATCH_H][PATCH_W], sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
-                smorph_pair<KW>(sx + c * g.window_elems(), sw + c * taps * OB + o, OB, s, scale, g, tx, ty, ref, sum, out);
+                const T* win = sx + (2 * c + (s < T(0) ? 1 : 0)) * welems;
+                T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
+                smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, scale, g, tx, ty, ref, inv_sum, out);
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -247,7 +279,7 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     a.g.replicate = false;  // out-of-image taps are excluded, never read
     a.x = x; a.w = w; a.alpha = alpha; a.y = y; a.target = target; a.counts = counts; a.merge = d.merge;
     a.o_groups = (d.Co + OB - 1) / OB;
-    const size_t per_channel = (static_cast<size_t>(a.g.window_elems()) + static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);
+    const size_t per_channel = (2 * static_cast<size_t>(a.g.window_elems()) + static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);
     if (per_channel > MAX_SHARED_BYTES)
     {
         set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
@@ -280,7 +312,8 @@ struct SmorphBackwardArgs
     T* gw;
     T* galpha;
     int merge;
-    T scale;  // 1 / Ci for AVERAGE
+    int o_chunk;      // output channels whose weights and bins are staged together
+    T scale;          // 1 / Ci for AVERAGE
 };
 
 template <typename T>
@@ -291,139 +324,234 @@ __device__ __forceinline__ T warp_sum(T v)
     return v;
 }
 
-/// CTA = (batch element, input channel, tile), looping over the output channels. Per pair the forward
-/// state (ref, S, out) is recomputed, then every tap k of every pixel contributes
+/// Backward of one pair for the thread's patch. Recomputes the forward state (ref, S, out), then every tap
+/// k of every pixel contributes
 ///     c_k = p_k g + alpha p_k g (v_k - out),   p_k g = e_k (g / S)
-/// to grad_input (at the pixel the tap read, accumulated in a shared gradient window) and to grad_weight
-/// (summed over the warp, then per-warp private bins), and p_k g (v_k - ref)(v_k - out) to grad_alpha
-/// (csrc/cpp/smorph_cpu_kernels.hxx:149-206). In the u domain alpha (v_k - out) = |alpha| (u_k - out_u) and
-/// (v_k - ref)(v_k - out) = (u_k - ref_u)(u_k - out_u).
-template <typename T, int KW>
-__global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_backward_kernel(const SmorphBackwardArgs<T> a)
+/// to grad_input at the pixel the tap read and to grad_weight, and p_k g (v_k - ref)(v_k - out) to
+/// grad_alpha (csrc/cpp/smorph_cpu_kernels.hxx:149-206). In the u domain alpha (v_k - out) = |alpha| (u_k - out_u)
+/// and (v_k - ref)(v_k - out) = (u_k - ref_u)(u_k - out_u); c_k is the gradient with respect to s x and s w,
+/// so the caller multiplies the sums by s. Excluded taps have e_k = 0 exactly and contribute exact zeros.
+/// grad_input: with KH > 0 every tap offset is a compile-time constant and the contributions are summed in
+/// the thread's register window gxr (patch + halo); otherwise they go to the shared window with atomics.
+/// grad_weight: the 8 pixels of the thread, then the warp, are summed per tap; lane 0 stores the warp's
+/// total in the warp's private bins (no atomics, no barrier).
+template <int KH, int KW, typename T, int GH, int GW>
+__device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ sg, T* __restrict__ wbin,
+                                                     T* __restrict__ abin, T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
+                                                     const Geometry& g, int tx, int ty, int lane, T (&gxr)[GH][GW])
+{
+    const int kwr = KW > 0 ? KW : g.kW;
+    T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
+    smorph_pair<0, KW>(win, swk, 1, scale, g, tx, ty, ref, inv_sum, out);  // kernel rows not unrolled: smaller code, fewer live registers
+
+    // s g / S: the sign turns the gradient of out = s out_u into the gradient of out_u ... and back: c_k below
+    // is d out / d u_k times g, and d u_k / d x = s, so the two signs cancel for grad_input and grad_weight
+    // (which are with respect to x and w, not s x and s w) except through this single factor.
+    T scaled[PATCH_H][PATCH_W];
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++) scaled[rr][j] = grad[rr][j] * inv_sum[rr][j];
+
+    T alpha_sum = T(0), tap_sum = T(0);
+    int current = -1;
+    auto flush_tap = [&](int k) {
+        const T total = warp_sum(tap_sum);
+        if (lane == 0) wbin[k] = total;
+        tap_sum = T(0);
+    };
+    for_each_tap<KH, KW>(win, g, tx, ty, [&](int kh, int kw, int rr, int j, T xv) {
+        const int k = kh * kwr + kw;
+        if (k != current)
+        {
+            if (current >= 0) flush_tap(current);
+            current = k;
+        }
+        const T u = xv + swk[k];
+        const T d = u - ref[rr][j];
+        const T pg = soft_exp(d, scale) * scaled[rr][j];
+        const T centered = u - out[rr][j];
+        const T c = fma(abs_alpha * pg, centered, pg);
+        if constexpr (KH > 0) gxr[rr + KH - 1 - kh][j + KW - 1 - kw] += c;
+        else if (c != T(0)) atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + j + g.kW - 1 - kw, c);
+        tap_sum += c;
+        alpha_sum = fma(pg * d, centered, alpha_sum);
+    });
+    flush_tap(current);
+    alpha_sum = warp_sum(alpha_sum);
+    if (lane == 0) *abin = alpha_sum;
+    (void)s;
+}
+
+/// CTA = (batch element, input channel, tile), looping over the output channels in chunks: the sign-folded
+/// structuring elements and the per-warp gradient bins of a whole chunk live in shared memory, so the loop
+/// over the chunk's output channels runs without a barrier.
+template <typename T, int KH, int KW>
+__global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) smorph_backward_kernel(const SmorphBackwardArgs<T> a)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int WARPS = THREADS / 32;
+    constexpr int GH = KH > 0 ? PATCH_H + KH - 1 : 1, GW = KH > 0 ? PATCH_W + KW - 1 : 1;
     const Geometry& g = a.g;
     const int taps = g.taps();
-    T* sx = reinterpret_cast<T*>(smem_raw);
-    T* sg = sx + g.window_elems();
-    T* sw = sg + g.window_elems();        // [taps], sign folded
-    T* wbins = sw + (taps + 3) / 4 * 4;   // [WARPS][taps]
-    T* abins = wbins + WARPS * taps;      // [WARPS]
+    const int welems = g.window_elems();
+    const int OC = a.o_chunk;
+    T* sx = reinterpret_cast<T*>(smem_raw);   // [2][window]: x and -x
+    T* sg = sx + 2 * welems;                   // gradient window of pairs with alpha >= 0, then of alpha < 0
+    T* sw = sg + 2 * welems;                   // [OC][taps], sign folded
+    T* spar = sw + OC * taps;                  // [OC][3]: sign, |alpha|, exp scale
+    T* wbins = spar + OC * 3;                  // [WARPS][OC][taps]
+    T* abins = wbins + WARPS * OC * taps;      // [WARPS][OC]
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int ci = blockIdx.x % g.Ci;
     const int tile = (blockIdx.x / g.Ci) % tiles;
     const int b = blockIdx.x / (g.Ci * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    const int tx = threadIdx.x % (TILE_W / PATCH_W), ty = threadIdx.x / (TILE_W / PATCH_W);
+    int tx, ty;
+    bool warp_live;
+    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t plane = g.plane();
     const int wci = g.identity ? 1 : g.Ci;
     const int wi = g.identity ? 0 : ci;
     const bool winner_takes_all = a.merge == MC_MERGE_MAX || a.merge == MC_MERGE_MIN;
-    const T nan = __longlong_as_double(0x7ff8000000000000LL);
-
-    load_window(sx, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0, tile_w0, nan);
-    for (int e = threadIdx.x; e < g.window_elems(); e += THREADS) sg[e] = T(0);
-
     const int o_begin = g.identity ? ci : 0;
     const int o_end = g.identity ? ci + 1 : g.Co;
-    for (int o = o_begin; o < o_end; o++)
+
+    bool has_pos = false, has_neg = false;
+    for (int o = o_begin + threadIdx.x; o < o_end; o += THREADS)
     {
-        const int pair = g.identity ? o : o * g.Ci + ci;
-        const T al = __ldg(a.alpha + pair);
-        const T s = al >= T(0) ? T(1) : T(-1);
-        const T abs_alpha = al >= T(0) ? al : -al;
-        const T scale = exp_scale(abs_alpha);
-        __syncthreads();
-        for (int k = threadIdx.x; k < taps; k += THREADS)
-        {
-            const T v = __ldg(a.w + (static_cast<int64_t>(o) * wci + wi) * taps + k);
-            sw[k] = s * v;
-        }
-        for (int e = threadIdx.x; e < WARPS * taps + WARPS; e += THREADS) wbins[e] = T(0);
-        __syncthreads();
+        const T al = __ldg(a.alpha + (g.identity ? o : static_cast<int64_t>(o) * g.Ci + ci));
+        has_pos |= al >= T(0);
+        has_neg |= al < T(0);
+    }
+    has_pos = __syncthreads_or(has_pos);
+    has_neg = __syncthreads_or(has_neg);
+    load_window_signed(has_pos ? sx : nullptr, has_neg ? sx + welems : nullptr, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0,
+                       tile_w0);
+    for (int e = threadIdx.x; e < 2 * welems; e += THREADS) sg[e] = T(0);
 
-        T ref[PATCH_H][PATCH_W], sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
-        smorph_pair<KW>(sx, sw, 1, s, scale, g, tx, ty, ref, sum, out);
-
-        // scaled = g / S for the pixels of the image; pixels of a partial tile that lie outside it are
-        // dead: their forward state may be inf or NaN and must not reach any sum.
-        T scaled[PATCH_H][PATCH_W];
-        bool live[PATCH_H][PATCH_W];
+    bool live[PATCH_H][PATCH_W];
+    int64_t at0[PATCH_H];
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+    {
+        const int h = tile_h0 + ty * PATCH_H + rr;
+        at0[rr] = (static_cast<int64_t>(b) * g.Co * g.H + h) * g.W + tile_w0 + tx * PATCH_W;
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++) live[rr][j] = h < g.H && tile_w0 + tx * PATCH_W + j < g.W;
+    }
+    auto load_grad = [&](int o, T (&dst)[PATCH_H][PATCH_W]) {
 #pragma unroll
         for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-            for (int j = 0; j < PATCH_W; j++)
-            {
-                const int h = tile_h0 + ty * PATCH_H + rr, w = tile_w0 + tx * PATCH_W + j;
-                live[rr][j] = h < g.H && w < g.W;
-                T grad = T(0);
-                if (live[rr][j])
-                {
-                    const int64_t at = ((static_cast<int64_t>(b) * g.Co + o) * g.H + h) * g.W + w;
-                    grad = __ldg(a.gy + at) * a.scale;
-                    if (winner_takes_all)
-                    {
-                        const T winners = __ldg(a.counts + at);
-                        grad = grad / (winners > T(0) ? winners : T(1));
-                        const T dist = s * out[rr][j] - __ldg(a.y + at);
-                        if (!(dist < T(1e-6) && dist > -T(1e-6))) grad = T(0);
-                    }
-                }
-                scaled[rr][j] = live[rr][j] ? grad * (T(1) / sum[rr][j]) : T(0);
-            }
+            for (int j = 0; j < PATCH_W; j++) dst[rr][j] = live[rr][j] ? __ldg(a.gy + at0[rr] + static_cast<int64_t>(o) * plane + j) * a.scale : T(0);
+    };
 
-        T alpha_sum = T(0);
-        T tap_sum = T(0);
-        int current = -1;
-        // Taps are visited in order, 8 pixels per tap: when the tap index changes, the finished tap's
-        // sum is reduced over the warp and stored by lane 0 in the warp's private bin.
-        auto flush_tap = [&](int k) {
-            const T total = warp_sum(tap_sum);
-            if (lane == 0) wbins[warp * taps + k] = total;
-            tap_sum = T(0);
-        };
-        for_each_tap<KW>(sx, g, tx, ty, [&](int k, int rr, int j, T xv) {
-            if (k != current)
-            {
-                if (current >= 0) flush_tap(current);
-                current = k;
-            }
-            const T u = fma(s, xv, sw[k]);
-            const bool valid = u == u && live[rr][j];  // the tap reads a pixel of the image, for a pixel of the image
-            const T d = valid ? u - ref[rr][j] : T(0);
-            const T e = valid ? soft_exp(d, scale) : T(0);
-            const T pg = e * scaled[rr][j];
-            const T centered = valid ? u - out[rr][j] : T(0);
-            const T c = fma(abs_alpha * pg, centered, pg);
-            if (c != T(0))
-            {
-                const int kh = k / g.kW, kw = k % g.kW;
-                atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + j + g.kW - 1 - kw, c);
-            }
-            tap_sum += c;
-            alpha_sum = fma(pg * d, centered, alpha_sum);
-        });
-        flush_tap(current);
-        alpha_sum = warp_sum(alpha_sum);
-        if (lane == 0) abins[warp] = alpha_sum;
+    // Register gradient windows, one per sign: contributions are gradients with respect to s x.
+    T gxr_pos[GH][GW], gxr_neg[GH][GW];
+#pragma unroll
+    for (int r = 0; r < GH; r++)
+#pragma unroll
+        for (int c = 0; c < GW; c++) gxr_pos[r][c] = gxr_neg[r][c] = T(0);
+
+    for (int oc0 = o_begin; oc0 < o_end; oc0 += OC)
+    {
+        const int oc = min(OC, o_end - oc0);
         __syncthreads();
-        for (int k = threadIdx.x; k < taps; k += THREADS)
+        for (int e = threadIdx.x; e < oc; e += THREADS)
+        {
+            const T al = __ldg(a.alpha + (g.identity ? oc0 + e : static_cast<int64_t>(oc0 + e) * g.Ci + ci));
+            const T ab = al >= T(0) ? al : -al;
+            spar[e * 3] = al >= T(0) ? T(1) : T(-1);
+            spar[e * 3 + 1] = ab;
+            spar[e * 3 + 2] = exp_scale(ab);
+        }
+        for (int e = threadIdx.x; e < oc * taps; e += THREADS)
+        {
+            const int k = e % taps, oo = e / taps;
+            const T al = __ldg(a.alpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci));
+            const T v = __ldg(a.w + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps + k);
+            sw[e] = al >= T(0) ? v : -v;
+        }
+        for (int e = threadIdx.x; e < WARPS * OC * (taps + 1); e += THREADS) wbins[e] = T(0);  // bins of warps that skip stay zero
+        __syncthreads();
+
+        if (warp_live)
+        {
+            T grad[PATCH_H][PATCH_W], next[PATCH_H][PATCH_W];
+            load_grad(oc0, grad);
+            for (int oo = 0; oo < oc; oo++)
+            {
+                const int o = oc0 + oo;
+                if (oo + 1 < oc) load_grad(o + 1, next);  // the next channel's gradients arrive while this one computes
+                const T s = spar[oo * 3], abs_alpha = spar[oo * 3 + 1], scale = spar[oo * 3 + 2];
+                const bool neg = s < T(0);
+                const T* win = sx + (neg ? welems : 0);
+                T* wbin = wbins + (warp * OC + oo) * taps;
+                T* abin = abins + warp * OC + oo;
+                if (winner_takes_all)
+                {
+                    // MAX / MIN: only the channels within 1e-6 of the merged value receive gradient, shared
+                    // equally; the pair's own soft extremum is needed first.
+                    T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
+                    smorph_pair<0, KW>(win, sw + oo * taps, 1, scale, g, tx, ty, ref, inv_sum, out);
+#pragma unroll
+                    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                        for (int j = 0; j < PATCH_W; j++)
+                        {
+                            if (!live[rr][j]) continue;
+                            const int64_t at = at0[rr] + static_cast<int64_t>(o) * plane + j;
+                            const T winners = __ldg(a.counts + at);
+                            const T dist = s * out[rr][j] - __ldg(a.y + at);
+                            grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
+                        }
+                }
+                // out = s out_u, so the gradient reaching out_u is s g.
+#pragma unroll
+                for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                    for (int j = 0; j < PATCH_W; j++) grad[rr][j] *= s;
+                if (neg) smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg + welems, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr_neg);
+                else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr_pos);
+#pragma unroll
+                for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                    for (int j = 0; j < PATCH_W; j++) grad[rr][j] = next[rr][j];
+            }
+        }
+        __syncthreads();
+        // The bins hold gradients with respect to s w and, for alpha, sums of s g (...): multiply by s.
+        for (int e = threadIdx.x; e < oc * taps; e += THREADS)
+        {
+            const int k = e % taps, oo = e / taps;
+            T total = T(0);
+#pragma unroll
+            for (int wp = 0; wp < WARPS; wp++) total += wbins[(wp * OC + oo) * taps + k];
+            if (total != T(0)) atomic_add(a.gw + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps + k, spar[oo * 3] * total);
+        }
+        for (int oo = threadIdx.x; oo < oc; oo += THREADS)
         {
             T total = T(0);
 #pragma unroll
-            for (int wp = 0; wp < WARPS; wp++) total += wbins[wp * taps + k];
-            if (total != T(0)) atomic_add(a.gw + (static_cast<int64_t>(o) * wci + wi) * taps + k, total);
+            for (int wp = 0; wp < WARPS; wp++) total += abins[wp * OC + oo];
+            if (total != T(0)) atomic_add(a.galpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci), spar[oo * 3] * total);
         }
-        if (threadIdx.x == 0)
-        {
-            T total = T(0);
+    }
+
+    if constexpr (KH > 0)
+    {
+        // One pass of shared atomics per CTA: the register windows of neighbouring threads overlap.
 #pragma unroll
-            for (int wp = 0; wp < WARPS; wp++) total += abins[wp];
-            if (total != T(0)) atomic_add(a.galpha + pair, total);
-        }
+        for (int r = 0; r < GH; r++)
+#pragma unroll
+            for (int c = 0; c < GW; c++)
+            {
+                const T v = gxr_pos[r][c] - gxr_neg[r][c];  // d(s x)/dx = s
+                if (v != T(0)) atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + c, v);
+            }
     }
     __syncthreads();
 
@@ -437,16 +565,18 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_backwa
         for (int c = lane; c < used_cols; c += 32)
         {
             const int ix = col0 + c;
-            const T v = sg[r * g.win_stride + c];
+            T v = sg[r * g.win_stride + c];
+            if constexpr (KH == 0) v -= sg[welems + r * g.win_stride + c];
             if (ix >= 0 && ix < g.W && v != T(0)) atomic_add(gxp + static_cast<int64_t>(iy) * g.W + ix, v);
         }
     }
 }
 
-template <typename T, int KW>
+template <typename T, int KH, int KW>
 int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* y, const T* counts, const T* gy, T* gx, T* gw,
                            T* galpha, cudaStream_t stream)
 {
+    constexpr int WARPS = THREADS / 32;
     SmorphBackwardArgs<T> a;
     a.g = make_geometry(d, sizeof(T));
     a.g.replicate = false;  // out-of-image taps are excluded, never read
@@ -454,15 +584,22 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     a.merge = d.merge;
     a.scale = d.merge == MC_MERGE_AVERAGE ? T(1.0) / static_cast<T>(d.Ci) : T(1.0);
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
-    const size_t smem = (2 * static_cast<size_t>(a.g.window_elems()) + (taps + 3) / 4 * 4 + (THREADS / 32) * (taps + 1)) * sizeof(T);
-    if (smem > MAX_SHARED_BYTES)
+    const size_t fixed = 4 * static_cast<size_t>(a.g.window_elems()) * sizeof(T);
+    const size_t per_o = (taps + 3 + WARPS * (taps + 1)) * sizeof(T);
+    if (fixed + per_o > MAX_SHARED_BYTES)
     {
         set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
         return MC_ERR_UNSUPPORTED;
     }
+    // Chunk of output channels: as many as fit in about 100 KiB (two CTAs per SM).
+    const size_t budget = fixed + per_o > 100 * 1024 ? MAX_SHARED_BYTES : 100 * 1024;
+    int chunk = static_cast<int>((budget - fixed) / per_o);
+    chunk = std::max(1, std::min(chunk, a.g.identity ? 1 : d.Co));
+    a.o_chunk = chunk;
+    const size_t smem = fixed + per_o * chunk;
     const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * d.Ci * d.B;
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
-    auto kernel = smorph_backward_kernel<T, KW>;
+    auto kernel = smorph_backward_kernel<T, KH, KW>;
     if (!allow_shared(kernel, smem)) { set_last_error("cannot opt in to %zu bytes of shared memory", smem); return MC_ERR_UNSUPPORTED; }
     kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a);
     return check_launch("smorph_backward_kernel");

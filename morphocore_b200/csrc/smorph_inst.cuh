@@ -45,9 +45,17 @@ int smorph_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const 
         if (rc != MC_OK) return rc;
         counts = static_cast<const T*>(ws);
     }
+    // Square 3, 5 and 7 structuring elements keep grad_input in registers (float only: the double
+    // kernels are bound by exp() and keep the smaller code).
+    if (sizeof(T) == 4 && d.kH == d.kW)
+    {
+        if (d.kW == 3) return launch_smorph_backward<T, 3, 3>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
+        if (d.kW == 5) return launch_smorph_backward<T, 5, 5>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
+        if (d.kW == 7) return launch_smorph_backward<T, 7, 7>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
+    }
     return dispatch_kernel_width(d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
-        return launch_smorph_backward<T, KW>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
+        return launch_smorph_backward<T, 0, KW>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
     });
 }
 
