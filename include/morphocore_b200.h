@@ -113,6 +113,11 @@ int mc_smorph_backward(const mc_desc* desc, const void* x, const void* w, const 
 const char* mc_status_string(int status);
 const char* mc_last_error(void);
 
+/* Number of thread blocks, on the current device since the library was loaded, whose bounded wait on an
+ * asynchronous (TMA) copy ran out and which therefore returned early: 0 in a healthy run. Synchronises
+ * the device; negative mc_status on failure. No counterpart in the reference (its kernels do not wait). */
+int mc_device_error_count(void);
+
 /* Number of kernels this library has launched in the calling process since it was loaded. */
 uint64_t mc_launch_count(void);
 

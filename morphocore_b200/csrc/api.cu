@@ -4,9 +4,29 @@
 #include <cstdio>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace mc
 {
+
+static __device__ unsigned int g_device_error = 0;
+
+unsigned int* device_error_counter()
+{
+    constexpr int MAX_DEVICES = 64;
+    static std::atomic<unsigned int*> cache[MAX_DEVICES];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return nullptr;
+    unsigned int* p = cache[device].load(std::memory_order_acquire);
+    if (p == nullptr)
+    {
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, g_device_error) != cudaSuccess) return nullptr;
+        p = static_cast<unsigned int*>(address);
+        cache[device].store(p, std::memory_order_release);
+    }
+    return p;
+}
 
 static thread_local char g_last_error[512] = "";
 static std::atomic<uint64_t> g_launches{0};
@@ -187,6 +207,17 @@ const char* mc_status_string(int status)
 }
 
 const char* mc_last_error(void) { return g_last_error; }
+
+int mc_device_error_count(void)
+{
+    unsigned int count = 0;
+    if (cudaMemcpyFromSymbol(&count, g_device_error, sizeof(count)) != cudaSuccess)
+    {
+        set_last_error("cudaMemcpyFromSymbol: %s", cudaGetErrorString(cudaGetLastError()));
+        return MC_ERR_CUDA;
+    }
+    return static_cast<int>(count);
+}
 
 uint64_t mc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

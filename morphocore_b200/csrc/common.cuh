@@ -8,8 +8,9 @@
 // its arithmetic. The shared window of a tile holds the tile plus the halo of the
 // structuring element with the border already resolved:
 //     window row r    <-> image row  tile_h0 - (kH - 1 - kH/2) + r
-//     window column c <-> image col  tile_w0 - (kW - 1 - kW/2) + c
-// so that tap (kh, kw) of the output pixel at tile offset (y, x) reads window (y + kH-1-kh, x + kW-1-kw),
+//     window column c <-> image col  tile_w0 - left + c,  left = (kW - 1 - kW/2) rounded up to 16 bytes
+// so that tap (kh, kw) of the output pixel at tile offset (y, x) reads window (y + kH-1-kh, off + x + kW-1-kw)
+// with off = left - (kW - 1 - kW/2),
 // which is image pixel (h + kH/2 - kh, w + kW/2 - kw): the reference's tap convention
 // (morphocore/functional/csrc/cuda/morpho_cuda_common.cuh:19, csrc/cpp/morpho_op_cpu_kernels.hxx:256-265).
 #pragma once
@@ -30,11 +31,26 @@ constexpr int THREADS = 256;
 constexpr int PATCH_W = 4;  // output pixels per thread along a row
 constexpr int PATCH_H = 2;  // output rows per thread
 
-/// Registers per thread row segment: the patch plus the kernel width, rounded up to whole 128-bit loads.
+/// Columns a tap can reach to the left of its pixel: tap kw of pixel w reads column w + kW/2 - kw.
+__host__ __device__ constexpr int halo_left_of(int kw) { return kw - 1 - kw / 2; }
+
+/// The window starts this many columns left of the tile: the left halo rounded up to a 16-byte multiple,
+/// so that the window's first column is a legal TMA x coordinate and rows stay 128-bit aligned.
+__host__ __device__ constexpr int halo_left_aligned(int kw, int elem_bytes)
+{
+    const int per_vec = 16 / elem_bytes;
+    return (halo_left_of(kw) + per_vec - 1) / per_vec * per_vec;
+}
+
+/// Unused columns at the start of every thread's row segment (the alignment slack above).
+__host__ __device__ constexpr int segment_offset(int kw, int elem_bytes) { return halo_left_aligned(kw, elem_bytes) - halo_left_of(kw); }
+
+/// Registers per thread row segment: the slack, the patch and the kernel width, rounded up to whole 128-bit
+/// loads. Tap kw of patch pixel j is element segment_offset + j + kW - 1 - kw.
 __host__ __device__ constexpr int segment_len(int kw, int elem_bytes)
 {
     const int per_vec = 16 / elem_bytes;
-    return (PATCH_W + kw - 1 + per_vec - 1) / per_vec * per_vec;
+    return (segment_offset(kw, elem_bytes) + PATCH_W + kw - 1 + per_vec - 1) / per_vec * per_vec;
 }
 
 /// Row stride of the shared window, in elements: every thread may read a whole segment.
@@ -50,6 +66,8 @@ struct Geometry
     int tiles_x, tiles_y;
     int win_rows;      // TILE_H + kH - 1
     int win_stride;    // window_stride(kW)
+    int seg_off;       // segment_offset(kW)
+    int left;          // halo_left_aligned(kW): window column 0 is image column tile_w0 - left
     int64_t weight_batch_stride;
     bool replicate;
     bool identity;
@@ -58,7 +76,8 @@ struct Geometry
     __host__ __device__ int64_t plane() const { return static_cast<int64_t>(H) * W; }
     __host__ __device__ int window_elems() const { return win_rows * win_stride; }
     __host__ __device__ int halo_top() const { return kH - 1 - pH; }
-    __host__ __device__ int halo_left() const { return kW - 1 - pW; }
+    __host__ __device__ int halo_left() const { return left; }
+    __host__ __device__ int used_cols() const { return seg_off + TILE_W + kW - 1; }
 };
 
 inline Geometry make_geometry(const mc_desc& d, int elem_bytes)
@@ -70,6 +89,8 @@ inline Geometry make_geometry(const mc_desc& d, int elem_bytes)
     g.tiles_y = (d.H + TILE_H - 1) / TILE_H;
     g.win_rows = TILE_H + d.kH - 1;
     g.win_stride = window_stride(d.kW, elem_bytes);
+    g.seg_off = segment_offset(d.kW, elem_bytes);
+    g.left = halo_left_aligned(d.kW, elem_bytes);
     g.weight_batch_stride = d.weight_batch_stride;
     g.replicate = d.pad_kind == MC_PAD_REPLICATE;
     g.identity = d.merge == MC_MERGE_IDENTITY;

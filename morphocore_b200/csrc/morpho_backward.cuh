@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
 
             if constexpr (KW > 0)
             {
-                constexpr int LEN = segment_len(KW, sizeof(T));
+                constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T));
                 for (int kh = 0; kh < g.kH; kh++)
                 {
                     T seg[PATCH_H][LEN];
@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
 #pragma unroll
                                 for (int j = 0; j < PATCH_W; j++)
                                 {
-                                    const T v = seg[rr][j + KW - 1 - kw] + wv[o];
+                                    const T v = seg[rr][OFF + j + KW - 1 - kw] + wv[o];
                                     if (strictly_better<IS_MIN>(v, best[o][rr][j]))
                                     {
                                         best[o][rr][j] = v;
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
 #pragma unroll
                             for (int j = 0; j < PATCH_W; j++)
                             {
-                                const T xv = row0[rr * g.win_stride + j + g.kW - 1 - kw];
+                                const T xv = row0[rr * g.win_stride + g.seg_off + j + g.kW - 1 - kw];
 #pragma unroll
                                 for (int o = 0; o < OB; o++)
                                 {
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
                         if (v == T(0)) continue;
                         const int k = arg[o][rr][j];
                         const int kh = KW > 0 ? k / KW : k / g.kW, kw = KW > 0 ? k % KW : k % g.kW;
-                        atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + j + g.kW - 1 - kw, v);
+                        atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + g.seg_off + j + g.kW - 1 - kw, v);
                         atomic_add(bins + (o * taps + k) * a.copies + lane_copy, v);
                     }
         }
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
     // Flush the gradient window; elements outside the image are the padding and are dropped.
     T* gxp = a.gx + (static_cast<int64_t>(b) * g.Ci + ci) * plane;
     const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
-    const int used_cols = TILE_W + g.kW - 1;
+    const int used_cols = g.used_cols();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int r = warp; r < g.win_rows; r += THREADS / 32)
     {

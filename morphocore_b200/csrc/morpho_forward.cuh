@@ -13,6 +13,7 @@
 // negated structuring element, x + (-w) being the same IEEE operation as x - w.
 #pragma once
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace mc
 {
@@ -30,6 +31,7 @@ struct ForwardArgs
     int o_groups;
     int chunk;      // input channels staged per barrier
     bool vec_store; // y rows are 16-byte aligned
+    unsigned int* errors;  // counter of timed-out waits
 };
 
 template <int OB, typename T>
@@ -55,7 +57,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
 {
     if constexpr (KW > 0)
     {
-        constexpr int LEN = segment_len(KW, sizeof(T));
+        constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T));
         for (int kh = 0; kh < g.kH; kh++)
         {
             T seg[PATCH_H][LEN];
@@ -75,7 +77,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
                         for (int j = 0; j < PATCH_W; j++)
-                            acc[o][rr][j] = ext3<IS_MIN>(acc[o][rr][j], seg[rr][j + KW - 1 - kw] + w0[o], seg[rr][j + KW - 2 - kw] + w1[o]);
+                            acc[o][rr][j] = ext3<IS_MIN>(acc[o][rr][j], seg[rr][OFF + j + KW - 1 - kw] + w0[o], seg[rr][OFF + j + KW - 2 - kw] + w1[o]);
             }
             if constexpr (KW & 1)
             {
@@ -86,7 +88,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                        for (int j = 0; j < PATCH_W; j++) acc[o][rr][j] = ext2<IS_MIN>(acc[o][rr][j], seg[rr][j] + w0[o]);
+                        for (int j = 0; j < PATCH_W; j++) acc[o][rr][j] = ext2<IS_MIN>(acc[o][rr][j], seg[rr][OFF + j] + w0[o]);
             }
         }
     }
@@ -105,7 +107,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
 #pragma unroll
                     for (int j = 0; j < PATCH_W; j++)
                     {
-                        const T xv = row0[rr * g.win_stride + j + g.kW - 1 - kw];
+                        const T xv = row0[rr * g.win_stride + g.seg_off + j + g.kW - 1 - kw];
 #pragma unroll
                         for (int o = 0; o < OB; o++) acc[o][rr][j] = ext2<IS_MIN>(acc[o][rr][j], xv + w0[o]);
                     }
@@ -134,13 +136,17 @@ __device__ __forceinline__ void stage_weights(T* __restrict__ sw, const T* __res
     }
 }
 
-template <typename T, bool IS_MIN, int KW, int OB, bool TRACK>
-__global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1)) ? 1 : 2) morpho_forward_kernel(const ForwardArgs<T> a)
+template <typename T, bool IS_MIN, int KW, int OB, bool TRACK, bool USE_TMA>
+__global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1)) ? 1 : 2)
+    morpho_forward_kernel(const ForwardArgs<T> a, const __grid_constant__ CUtensorMap tmap)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const Geometry& g = a.g;
-    T* sx = reinterpret_cast<T*>(smem_raw);
-    T* sw = sx + a.chunk * g.window_elems();
+    // Layout: [2 mbarriers][pad to 128][stage 0 windows][stage 1 windows][weights]; a single stage without TMA.
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
+    const int stage_elems = (a.chunk * g.window_elems() * static_cast<int>(sizeof(T)) + 127) / 128 * 128 / static_cast<int>(sizeof(T));
+    T* sx0 = reinterpret_cast<T*>(smem_raw + 128);
+    T* sw = sx0 + (USE_TMA ? 2 : 1) * stage_elems;
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int og = blockIdx.x % a.o_groups;
@@ -172,16 +178,60 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
                 if constexpr (TRACK) winner[o][rr][j] = 0;
             }
 
-    for (int c0 = 0; c0 < channels; c0 += a.chunk)
+    // TMA: chunk n + 1 is copied into the other stage while chunk n is computed. The copy zero fills
+    // outside the image; tiles whose window leaves the image patch those elements for the other border rules.
+    const uint32_t stage_bytes = static_cast<uint32_t>(a.chunk) * g.window_elems() * sizeof(T);
+    const int first_channel = g.identity ? o0 : 0;
+    const bool fix_border = USE_TMA && (g.replicate || a.fill != T(0)) && window_leaves_image(g, tile_h0, tile_w0);
+    auto issue = [&](int n) {
+        uint64_t* bar = full + (n & 1);
+        mbar_expect_tx(bar, stage_bytes);
+        tma_load_4d(sx0 + (n & 1) * stage_elems, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), first_channel + n * a.chunk, b);
+    };
+    if constexpr (USE_TMA)
+    {
+        if (threadIdx.x == 0)
+        {
+            mbar_init(full, 1);
+            mbar_init(full + 1, 1);
+            mbar_fence_init();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) issue(0);
+    }
+
+    int n = 0;
+    for (int c0 = 0; c0 < channels; c0 += a.chunk, n++)
     {
         const int cc = min(a.chunk, channels - c0);
+        T* sx = sx0 + (USE_TMA ? (n & 1) * stage_elems : 0);
         __syncthreads();
-        for (int c = 0; c < cc; c++)
+        if constexpr (USE_TMA)
         {
-            const int ci = g.identity ? o0 : c0 + c;
-            load_window(sx + c * g.window_elems(), xb + static_cast<int64_t>(ci) * plane, g, tile_h0, tile_w0, a.fill);
+            if (threadIdx.x == 0 && c0 + a.chunk < channels)
+            {
+                fence_async_smem();
+                issue(n + 1);
+            }
+        }
+        else
+        {
+            for (int c = 0; c < cc; c++)
+            {
+                const int ci = g.identity ? o0 : c0 + c;
+                load_window(sx + c * g.window_elems(), xb + static_cast<int64_t>(ci) * plane, g, tile_h0, tile_w0, a.fill);
+            }
         }
         stage_weights<T, IS_MIN, OB>(sw, wb, g, o0, c0, cc);
+        if constexpr (USE_TMA)
+        {
+            if (!mbar_wait(full + (n & 1), (n >> 1) & 1))
+            {
+                if (threadIdx.x == 0 && a.errors != nullptr) atomicAdd(a.errors, 1u);
+                return;  // every thread of the CTA waits on the same barrier and gives up together
+            }
+            if (fix_border) fix_window_border(sx, xb + static_cast<int64_t>(first_channel + c0) * plane, plane, cc, g, tile_h0, tile_w0, a.fill);
+        }
         __syncthreads();
 
         for (int c = 0; c < cc && warp_live; c++)
@@ -293,41 +343,48 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
 
 template <typename T> struct ForwardPlan
 {
-    int ob;
     int chunk;
     size_t smem;
 };
 
-/// Channels staged per barrier: as many as fit in about 96 KiB (two CTAs per SM), at most 8.
+/// Channels staged per barrier: as many as fit in about 96 KiB (two CTAs per SM), at most 8; `stages`
+/// window buffers (2 with TMA double buffering) plus one buffer of structuring elements.
 template <typename T>
-inline bool plan_forward(const Geometry& g, int ob, ForwardPlan<T>& plan)
+inline bool plan_forward(const Geometry& g, int ob, int stages, ForwardPlan<T>& plan)
 {
-    const size_t per_channel = (static_cast<size_t>(g.window_elems()) + static_cast<size_t>(g.taps()) * ob) * sizeof(T);
-    if (per_channel > MAX_SHARED_BYTES) return false;
+    const size_t window = static_cast<size_t>(g.window_elems()) * sizeof(T), weights = static_cast<size_t>(g.taps()) * ob * sizeof(T);
+    const size_t per_channel = stages * window + weights;
+    const size_t fixed = 128 + stages * 128;
+    if (per_channel + fixed > MAX_SHARED_BYTES) return false;
     const int channels = g.identity ? 1 : g.Ci;
-    int chunk = static_cast<int>((96 * 1024) / per_channel);
+    int chunk = static_cast<int>((96 * 1024 - fixed) / per_channel);
     chunk = chunk < 1 ? 1 : (chunk > 8 ? 8 : chunk);
     chunk = chunk > channels ? channels : chunk;
-    plan.ob = ob;
     plan.chunk = chunk;
-    plan.smem = per_channel * chunk;
+    plan.smem = fixed + per_channel * chunk;
     return true;
+}
+
+template <typename T, bool IS_MIN, int KW, int OB, bool TRACK, bool USE_TMA>
+int launch_forward_variant(const ForwardArgs<T>& a, const CUtensorMap& tmap, int64_t blocks, size_t smem, cudaStream_t stream)
+{
+    auto kernel = morpho_forward_kernel<T, IS_MIN, KW, OB, TRACK, USE_TMA>;
+    if (!allow_shared(kernel, smem))
+    {
+        set_last_error("cannot opt in to %zu bytes of shared memory", smem);
+        return MC_ERR_UNSUPPORTED;
+    }
+    kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a, tmap);
+    return check_launch("morpho_forward_kernel");
 }
 
 template <typename T, bool IS_MIN, int KW, int OB>
 int launch_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx, cudaStream_t stream)
 {
     const Geometry g = make_geometry(d, sizeof(T));
-    ForwardPlan<T> plan;
-    if (!plan_forward<T>(g, OB, plan))
-    {
-        set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
-        return MC_ERR_UNSUPPORTED;
-    }
     ForwardArgs<T> a;
     a.g = g; a.x = x; a.w = w; a.y = y; a.idx = idx; a.merge = d.merge; a.fill = static_cast<T>(d.fill);
     a.o_groups = (d.Co + OB - 1) / OB;
-    a.chunk = plan.chunk;
     a.vec_store = (d.W % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
     const int64_t blocks = static_cast<int64_t>(g.tiles_x) * g.tiles_y * a.o_groups * d.B;
     if (blocks > 0x7fffffffLL)
@@ -336,14 +393,26 @@ int launch_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx,
         return MC_ERR_UNSUPPORTED;
     }
     const bool track = idx != nullptr;
-    auto kernel = track ? morpho_forward_kernel<T, IS_MIN, KW, OB, true> : morpho_forward_kernel<T, IS_MIN, KW, OB, false>;
-    if (!allow_shared(kernel, plan.smem))
+    a.errors = device_error_counter();
+
+    // TMA staging when the tensor can be described by a tensor map (16-byte row pitch and base).
+    ForwardPlan<T> plan;
+    CUtensorMap tmap{};
+    if (plan_forward<T>(g, OB, 2, plan)
+        && make_window_tensor_map(&tmap, x, sizeof(T), d.B, d.Ci, d.H, d.W, g.win_stride, g.win_rows, plan.chunk))
     {
-        set_last_error("cannot opt in to %zu bytes of shared memory", plan.smem);
+        a.chunk = plan.chunk;
+        return track ? launch_forward_variant<T, IS_MIN, KW, OB, true, true>(a, tmap, blocks, plan.smem, stream)
+                     : launch_forward_variant<T, IS_MIN, KW, OB, false, true>(a, tmap, blocks, plan.smem, stream);
+    }
+    if (!plan_forward<T>(g, OB, 1, plan))
+    {
+        set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
         return MC_ERR_UNSUPPORTED;
     }
-    kernel<<<static_cast<unsigned>(blocks), THREADS, plan.smem, stream>>>(a);
-    return check_launch("morpho_forward_kernel");
+    a.chunk = plan.chunk;
+    return track ? launch_forward_variant<T, IS_MIN, KW, OB, true, false>(a, tmap, blocks, plan.smem, stream)
+                 : launch_forward_variant<T, IS_MIN, KW, OB, false, false>(a, tmap, blocks, plan.smem, stream);
 }
 
 }  // namespace mc

@@ -49,7 +49,7 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
 {
     if constexpr (KW > 0)
     {
-        constexpr int LEN = segment_len(KW, sizeof(T));
+        constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T));
         auto row = [&](int kh, int top) {
             T seg[PATCH_H][LEN];
 #pragma unroll
@@ -60,7 +60,7 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++) f(kh, kw, rr, j, seg[rr][j + KW - 1 - kw]);
+                    for (int j = 0; j < PATCH_W; j++) f(kh, kw, rr, j, seg[rr][OFF + j + KW - 1 - kw]);
         };
         if constexpr (KH > 0)
         {
@@ -81,7 +81,7 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++) f(kh, kw, rr, j, row0[rr * g.win_stride + j + g.kW - 1 - kw]);
+                    for (int j = 0; j < PATCH_W; j++) f(kh, kw, rr, j, row0[rr * g.win_stride + g.seg_off + j + g.kW - 1 - kw]);
         }
     }
 }
@@ -373,7 +373,7 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
         const T centered = u - out[rr][j];
         const T c = fma(abs_alpha * pg, centered, pg);
         if constexpr (KH > 0) gxr[rr + KH - 1 - kh][j + KW - 1 - kw] += c;
-        else if (c != T(0)) atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + j + g.kW - 1 - kw, c);
+        else if (c != T(0)) atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + g.seg_off + j + g.kW - 1 - kw, c);
         tap_sum += c;
         alpha_sum = fma(pg * d, centered, alpha_sum);
     });
@@ -550,14 +550,14 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             for (int c = 0; c < GW; c++)
             {
                 const T v = gxr_pos[r][c] - gxr_neg[r][c];  // d(s x)/dx = s
-                if (v != T(0)) atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + c, v);
+                if (v != T(0)) atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + g.seg_off + c, v);
             }
     }
     __syncthreads();
 
     T* gxp = a.gx + (static_cast<int64_t>(b) * g.Ci + ci) * plane;
     const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
-    const int used_cols = TILE_W + g.kW - 1;
+    const int used_cols = g.used_cols();
     for (int r = warp; r < g.win_rows; r += WARPS)
     {
         const int iy = row0 + r;

@@ -1,0 +1,126 @@
+// TMA staging of tile windows: tensor-map creation on the host, mbarrier and cp.async.bulk.tensor wrappers
+// on the device. One 4-D tiled copy (no multicast) brings the windows of a whole chunk of input channels
+// of one tile into shared memory, out-of-image elements zero filled, while the CTA computes on the
+// previous chunk. Every wait on an mbarrier is bounded: when it runs out the kernel records the fact in
+// g_device_error and returns instead of spinning.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace mc
+{
+
+/// Device address, on the current device, of the counter a kernel increments when its bounded wait on a
+/// TMA copy runs out (read back with mc_device_error_count()); nullptr if it cannot be resolved.
+unsigned int* device_error_counter();
+
+/// Tensor map over a contiguous [B, C, H, W] tensor with a box of box_w x box_rows x box_c x 1 elements.
+/// Returns false when the tensor cannot be described (row pitch or base not a multiple of 16 bytes, the
+/// driver entry point is missing, or the driver rejects the shape): the caller then stages with plain loads.
+inline bool make_window_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int B, int C, int H, int W, int box_w, int box_rows,
+                                   int box_c)
+{
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = []() -> EncodeFn {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess || status != cudaDriverEntryPointSuccess)
+        {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeFn>(fn);
+    }();
+    if (encode == nullptr) return false;
+    const uint64_t row_bytes = static_cast<uint64_t>(W) * elem_bytes;
+    if (row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(base) % 16 != 0) return false;
+    if (box_w > 256 || box_rows > 256 || box_c > 256 || (static_cast<uint64_t>(box_w) * elem_bytes) % 16 != 0) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[3] = {row_bytes, row_bytes * H, row_bytes * H * C};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(box_w), static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_c), 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    const CUresult rc = encode(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 4, const_cast<void*>(base), dims,
+                               strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+
+/// Makes the barrier initialisation visible to the async proxy.
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+/// Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy copies.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+/// Bounded wait for the phase with the given parity. Each try suspends for a hardware-limited time; the
+/// loop gives up after about a second and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = smem_addr(bar);
+    for (int it = 0; it < (1 << 22); it++)
+    {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(addr), "r"(parity)
+                     : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+/// 4-D tiled TMA load (no multicast) of the box at (x, y, c, b) into shared memory; completion is
+/// signalled on `bar` by transaction bytes. x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int c, int b)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_addr(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(c), "r"(b)
+                 : "memory");
+}
+
+/// After a TMA copy of a window (zero filled outside the image): overwrite the out-of-image elements of
+/// `channels` staged windows with the border rule. Only CTAs whose window leaves the image call this.
+template <typename T>
+__device__ __forceinline__ void fix_window_border(T* __restrict__ win, const T* __restrict__ planes, int64_t plane_stride, int channels,
+                                                  const Geometry& g, int tile_h0, int tile_w0, T outside)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
+    for (int r = warp; r < g.win_rows * channels; r += THREADS / 32)
+    {
+        const int c = r / g.win_rows, wr = r % g.win_rows;
+        const int iy = row0 + wr;
+        const bool row_in = iy >= 0 && iy < g.H;
+        const T* src = planes + c * plane_stride + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W;
+        T* out = win + static_cast<int64_t>(c) * g.window_elems() + wr * g.win_stride;
+        for (int col = lane; col < g.win_stride; col += 32)
+        {
+            const int ix = col0 + col;
+            if (row_in && ix >= 0 && ix < g.W) continue;
+            out[col] = g.replicate ? __ldg(src + min(max(ix, 0), g.W - 1)) : outside;
+        }
+    }
+}
+
+__device__ __forceinline__ bool window_leaves_image(const Geometry& g, int tile_h0, int tile_w0)
+{
+    const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
+    return row0 < 0 || col0 < 0 || row0 + g.win_rows > g.H || col0 + g.win_stride > g.W;
+}
+
+}  // namespace mc
