@@ -127,6 +127,109 @@ __device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* 
 }
 
 template <typename T>
+__device__ __forceinline__ T warp_sum(T v)
+{
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// 3 x 3 structuring elements: everything about one pair and one 4-pixel row of the patch lives in
+// registers. The 9 values u_k of each pixel are formed once and serve the maximum, the exponentials and,
+// in the backward pass (which also keeps the 9 exponentials), the gradients: 7 to 8 issued instructions
+// per tap forward, of which one ex2, so the forward pass runs at the rate of the special-function unit.
+// ---------------------------------------------------------------------------------------------------
+
+/// u_k = xs + ws for the 4 pixels of patch row rr, k = kh * 3 + kw.
+template <typename T>
+__device__ __forceinline__ void smorph3_values(const T* __restrict__ win, const T* __restrict__ swk, int wstride, const Geometry& g, int tx, int ty,
+                                               int rr, T (&u)[9][PATCH_W])
+{
+    constexpr int LEN = segment_len(3, sizeof(T)), OFF = segment_offset(3, sizeof(T));
+#pragma unroll
+    for (int kh = 0; kh < 3; kh++)
+    {
+        T seg[LEN];
+        load_segment<LEN>(seg, win + (ty * PATCH_H + rr + 2 - kh) * g.win_stride + tx * PATCH_W);
+#pragma unroll
+        for (int kw = 0; kw < 3; kw++)
+        {
+            const T wv = swk[(kh * 3 + kw) * wstride];
+#pragma unroll
+            for (int j = 0; j < PATCH_W; j++) u[kh * 3 + kw][j] = seg[OFF + j + 2 - kw] + wv;
+        }
+    }
+}
+
+/// ref, e_k, 1 / S and out_u of 4 pixels from their u_k.
+template <typename T>
+__device__ __forceinline__ void smorph3_softmax(const T (&u)[9][PATCH_W], T scale, T (&ref)[PATCH_W], T (&e)[9][PATCH_W], T (&inv_sum)[PATCH_W],
+                                                T (&out)[PATCH_W])
+{
+#pragma unroll
+    for (int j = 0; j < PATCH_W; j++)
+    {
+        T m = ext3<false>(u[0][j], u[1][j], u[2][j]);
+        m = ext3<false>(m, u[3][j], u[4][j]);
+        m = ext3<false>(m, u[5][j], u[6][j]);
+        ref[j] = ext3<false>(m, u[7][j], u[8][j]);
+        T sum = T(0), weighted = T(0);
+#pragma unroll
+        for (int k = 0; k < 9; k++)
+        {
+            e[k][j] = soft_exp(u[k][j] - ref[j], scale);
+            sum += e[k][j];
+            weighted = fma(e[k][j], u[k][j], weighted);
+        }
+        inv_sum[j] = soft_rcp(sum);
+        out[j] = weighted * inv_sum[j];
+    }
+}
+
+/// Backward of one 3 x 3 pair for the thread's patch, see smorph_pair_backward.
+template <typename T>
+__device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ wbin, T* __restrict__ abin,
+                                                      T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W], const Geometry& g, int tx, int ty, int lane,
+                                                      T (&gxr)[PATCH_H + 2][PATCH_W + 2])
+{
+    T tap_sum[9];
+#pragma unroll
+    for (int k = 0; k < 9; k++) tap_sum[k] = T(0);
+    T alpha_sum = T(0);
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+    {
+        T u[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out[PATCH_W];
+        smorph3_values(win, swk, 1, g, tx, ty, rr, u);
+        smorph3_softmax(u, scale, ref, e, inv_sum, out);
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            const T scaled = grad[rr][j] * inv_sum[j];
+#pragma unroll
+            for (int k = 0; k < 9; k++)
+            {
+                const T pg = e[k][j] * scaled;
+                const T centered = u[k][j] - out[j];
+                const T c = fma(abs_alpha * pg, centered, pg);
+                gxr[rr + 2 - k / 3][j + 2 - k % 3] += c;
+                tap_sum[k] += c;
+                alpha_sum = fma(pg * (u[k][j] - ref[j]), centered, alpha_sum);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 9; k++)
+    {
+        const T total = warp_sum(tap_sum[k]);
+        if (lane == 0) wbin[k] = total;
+    }
+    alpha_sum = warp_sum(alpha_sum);
+    if (lane == 0) *abin = alpha_sum;
+}
+
+template <typename T>
 struct SmorphForwardArgs
 {
     Geometry g;
@@ -232,8 +335,22 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             {
                 const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
                 const T* win = sx + (2 * c + (s < T(0) ? 1 : 0)) * welems;
-                T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
-                smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, scale, g, tx, ty, ref, inv_sum, out);
+                T out[PATCH_H][PATCH_W];
+                if (KW == 3 && g.kH == 3)
+                {
+#pragma unroll
+                    for (int rr = 0; rr < PATCH_H; rr++)
+                    {
+                        T u[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W];
+                        smorph3_values(win, sw + c * taps * OB + o, OB, g, tx, ty, rr, u);
+                        smorph3_softmax(u, scale, ref, e, inv_sum, out[rr]);
+                    }
+                }
+                else
+                {
+                    T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
+                    smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, scale, g, tx, ty, ref, inv_sum, out);
+                }
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -316,37 +433,26 @@ struct SmorphBackwardArgs
     T scale;          // 1 / Ci for AVERAGE
 };
 
-template <typename T>
-__device__ __forceinline__ T warp_sum(T v)
-{
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    return v;
-}
-
 /// Backward of one pair for the thread's patch. Recomputes the forward state (ref, S, out), then every tap
 /// k of every pixel contributes
 ///     c_k = p_k g + alpha p_k g (v_k - out),   p_k g = e_k (g / S)
 /// to grad_input at the pixel the tap read and to grad_weight, and p_k g (v_k - ref)(v_k - out) to
 /// grad_alpha (csrc/cpp/smorph_cpu_kernels.hxx:149-206). In the u domain alpha (v_k - out) = |alpha| (u_k - out_u)
-/// and (v_k - ref)(v_k - out) = (u_k - ref_u)(u_k - out_u); c_k is the gradient with respect to s x and s w,
-/// so the caller multiplies the sums by s. Excluded taps have e_k = 0 exactly and contribute exact zeros.
+/// and (v_k - ref)(v_k - out) = (u_k - ref_u)(u_k - out_u), so with g the gradient of out itself the sums need
+/// no sign correction. Excluded taps have e_k = 0 exactly and contribute exact zeros.
 /// grad_input: with KH > 0 every tap offset is a compile-time constant and the contributions are summed in
 /// the thread's register window gxr (patch + halo); otherwise they go to the shared window with atomics.
 /// grad_weight: the 8 pixels of the thread, then the warp, are summed per tap; lane 0 stores the warp's
 /// total in the warp's private bins (no atomics, no barrier).
 template <int KH, int KW, typename T, int GH, int GW>
 __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ sg, T* __restrict__ wbin,
-                                                     T* __restrict__ abin, T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
+                                                     T* __restrict__ abin, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
                                                      const Geometry& g, int tx, int ty, int lane, T (&gxr)[GH][GW])
 {
     const int kwr = KW > 0 ? KW : g.kW;
     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
     smorph_pair<0, KW>(win, swk, 1, scale, g, tx, ty, ref, inv_sum, out);  // kernel rows not unrolled: smaller code, fewer live registers
 
-    // s g / S: the sign turns the gradient of out = s out_u into the gradient of out_u ... and back: c_k below
-    // is d out / d u_k times g, and d u_k / d x = s, so the two signs cancel for grad_input and grad_weight
-    // (which are with respect to x and w, not s x and s w) except through this single factor.
     T scaled[PATCH_H][PATCH_W];
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
@@ -380,7 +486,6 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
     flush_tap(current);
     alpha_sum = warp_sum(alpha_sum);
     if (lane == 0) *abin = alpha_sum;
-    (void)s;
 }
 
 /// CTA = (batch element, input channel, tile), looping over the output channels in chunks: the sign-folded
@@ -397,8 +502,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     const int welems = g.window_elems();
     const int OC = a.o_chunk;
     T* sx = reinterpret_cast<T*>(smem_raw);   // [2][window]: x and -x
-    T* sg = sx + 2 * welems;                   // gradient window of pairs with alpha >= 0, then of alpha < 0
-    T* sw = sg + 2 * welems;                   // [OC][taps], sign folded
+    T* sg = sx + 2 * welems;                   // gradient window
+    T* sw = sg + welems;                       // [OC][taps], sign folded
     T* spar = sw + OC * taps;                  // [OC][3]: sign, |alpha|, exp scale
     T* wbins = spar + OC * 3;                  // [WARPS][OC][taps]
     T* abins = wbins + WARPS * OC * taps;      // [WARPS][OC]
@@ -430,7 +535,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     has_neg = __syncthreads_or(has_neg);
     load_window_signed(has_pos ? sx : nullptr, has_neg ? sx + welems : nullptr, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0,
                        tile_w0);
-    for (int e = threadIdx.x; e < 2 * welems; e += THREADS) sg[e] = T(0);
+    for (int e = threadIdx.x; e < welems; e += THREADS) sg[e] = T(0);
 
     bool live[PATCH_H][PATCH_W];
     int64_t at0[PATCH_H];
@@ -449,12 +554,11 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             for (int j = 0; j < PATCH_W; j++) dst[rr][j] = live[rr][j] ? __ldg(a.gy + at0[rr] + static_cast<int64_t>(o) * plane + j) * a.scale : T(0);
     };
 
-    // Register gradient windows, one per sign: contributions are gradients with respect to s x.
-    T gxr_pos[GH][GW], gxr_neg[GH][GW];
+    T gxr[GH][GW];
 #pragma unroll
     for (int r = 0; r < GH; r++)
 #pragma unroll
-        for (int c = 0; c < GW; c++) gxr_pos[r][c] = gxr_neg[r][c] = T(0);
+        for (int c = 0; c < GW; c++) gxr[r][c] = T(0);
 
     for (int oc0 = o_begin; oc0 < o_end; oc0 += OC)
     {
@@ -509,13 +613,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
                         }
                 }
-                // out = s out_u, so the gradient reaching out_u is s g.
-#pragma unroll
-                for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-                    for (int j = 0; j < PATCH_W; j++) grad[rr][j] *= s;
-                if (neg) smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg + welems, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr_neg);
-                else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr_pos);
+                if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -523,21 +622,20 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             }
         }
         __syncthreads();
-        // The bins hold gradients with respect to s w and, for alpha, sums of s g (...): multiply by s.
         for (int e = threadIdx.x; e < oc * taps; e += THREADS)
         {
             const int k = e % taps, oo = e / taps;
             T total = T(0);
 #pragma unroll
             for (int wp = 0; wp < WARPS; wp++) total += wbins[(wp * OC + oo) * taps + k];
-            if (total != T(0)) atomic_add(a.gw + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps + k, spar[oo * 3] * total);
+            if (total != T(0)) atomic_add(a.gw + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps + k, total);
         }
         for (int oo = threadIdx.x; oo < oc; oo += THREADS)
         {
             T total = T(0);
 #pragma unroll
             for (int wp = 0; wp < WARPS; wp++) total += abins[wp * OC + oo];
-            if (total != T(0)) atomic_add(a.galpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci), spar[oo * 3] * total);
+            if (total != T(0)) atomic_add(a.galpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci), total);
         }
     }
 
@@ -548,10 +646,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
         for (int r = 0; r < GH; r++)
 #pragma unroll
             for (int c = 0; c < GW; c++)
-            {
-                const T v = gxr_pos[r][c] - gxr_neg[r][c];  // d(s x)/dx = s
-                if (v != T(0)) atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + g.seg_off + c, v);
-            }
+                if (gxr[r][c] != T(0)) atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + g.seg_off + c, gxr[r][c]);
     }
     __syncthreads();
 
@@ -565,8 +660,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
         for (int c = lane; c < used_cols; c += 32)
         {
             const int ix = col0 + c;
-            T v = sg[r * g.win_stride + c];
-            if constexpr (KH == 0) v -= sg[welems + r * g.win_stride + c];
+            const T v = sg[r * g.win_stride + c];
             if (ix >= 0 && ix < g.W && v != T(0)) atomic_add(gxp + static_cast<int64_t>(iy) * g.W + ix, v);
         }
     }
@@ -584,7 +678,7 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     a.merge = d.merge;
     a.scale = d.merge == MC_MERGE_AVERAGE ? T(1.0) / static_cast<T>(d.Ci) : T(1.0);
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
-    const size_t fixed = 4 * static_cast<size_t>(a.g.window_elems()) * sizeof(T);
+    const size_t fixed = 3 * static_cast<size_t>(a.g.window_elems()) * sizeof(T);
     const size_t per_o = (taps + 3 + WARPS * (taps + 1)) * sizeof(T);
     if (fixed + per_o > MAX_SHARED_BYTES)
     {
