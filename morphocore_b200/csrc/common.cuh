@@ -152,11 +152,12 @@ __device__ __forceinline__ void load_window(T* __restrict__ dst, const T* __rest
     }
 }
 
-/// Stage the window of one plane for the smorph kernels, whose taps outside the image are excluded: `pos`
-/// receives x and `neg` receives -x (either may be null), and both read -big outside the image, a value
-/// that never wins a maximum and whose exponential is exactly zero.
+/// Stage the window of one plane for the smorph kernels, whose taps outside the image are excluded. Both
+/// windows hold x inside the image; outside, `low` (read by pairs with alpha >= 0, u = x + w) holds -big and
+/// `high` (read by pairs with alpha < 0, u = -x - w) holds +big, so that u = -big there: a value that never
+/// wins the maximum and whose exponential is exactly zero. Either pointer may be null.
 template <typename T>
-__device__ __forceinline__ void load_window_signed(T* __restrict__ pos, T* __restrict__ neg, const T* __restrict__ plane, const Geometry& g,
+__device__ __forceinline__ void load_window_signed(T* __restrict__ low, T* __restrict__ high, const T* __restrict__ plane, const Geometry& g,
                                                    int tile_h0, int tile_w0)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -171,8 +172,8 @@ __device__ __forceinline__ void load_window_signed(T* __restrict__ pos, T* __res
             const int ix = col0 + c;
             const bool in = row_in && ix >= 0 && ix < g.W;
             const T v = in ? __ldg(src + ix) : T(0);
-            if (pos != nullptr) pos[r * g.win_stride + c] = in ? v : -Limits<T>::big();
-            if (neg != nullptr) neg[r * g.win_stride + c] = in ? -v : -Limits<T>::big();
+            if (low != nullptr) low[r * g.win_stride + c] = in ? v : -Limits<T>::big();
+            if (high != nullptr) high[r * g.win_stride + c] = in ? v : Limits<T>::big();
         }
     }
 }

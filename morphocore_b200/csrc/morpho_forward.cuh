@@ -310,34 +310,72 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
             }
             if constexpr (TRACK)
             {
-                // The winning channel is known; scan it alone for its first extremal tap, with the
-                // reference's strict comparison from the initial value (index 0 when nothing beats it).
-                const T* wo = wb + static_cast<int64_t>(o0 + o) * g.Ci * g.taps();
+                // Only the winning channel is known here; morpho_find_tap_kernel adds the tap.
 #pragma unroll
                 for (int j = 0; j < PATCH_W; j++)
+                    if (w0 + j < g.W) a.idx[row + w0 + j] = winner[o][rr][j] << 16;
+            }
+        }
+    }
+}
+
+/// Second step of the winner index of MAX / MIN merges: one thread per output pixel scans the winning
+/// channel alone for its first extremal tap, with the reference's strict comparison from the initial
+/// value in kh-major, kw order (index 0 when nothing beats it), and completes idx to (channel << 16) | tap.
+/// Running it as its own launch keeps every SM full of independent gathers instead of serialising them at
+/// the end of the tile kernel.
+template <typename T, bool IS_MIN>
+__global__ void __launch_bounds__(THREADS) morpho_find_tap_kernel(const ForwardArgs<T> a, int64_t total)
+{
+    const Geometry& g = a.g;
+    const int64_t plane = g.plane();
+    const int taps = g.taps();
+    const T op_init = IS_MIN ? Limits<T>::inf() : -Limits<T>::inf();
+    for (int64_t at = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; at < total; at += static_cast<int64_t>(gridDim.x) * THREADS)
+    {
+        const int w = static_cast<int>(at % g.W), h = static_cast<int>((at / g.W) % g.H);
+        const int o = static_cast<int>((at / plane) % g.Co), b = static_cast<int>(at / (plane * g.Co));
+        int ch = a.idx[at] >> 16;
+        ch = min(max(ch, 0), g.Ci - 1);
+        const T* xp = a.x + (static_cast<int64_t>(b) * g.Ci + ch) * plane;
+        const T* wk = a.w + static_cast<int64_t>(b) * g.weight_batch_stride + (static_cast<int64_t>(o) * g.Ci + ch) * taps;
+        T best = op_init;
+        int arg = 0;
+        const bool inside = h - (g.kH - 1 - g.pH) >= 0 && h + g.pH < g.H && w - (g.kW - 1 - g.pW) >= 0 && w + g.pW < g.W;
+        if (inside)
+        {
+            for (int kh = 0; kh < g.kH; kh++)
+            {
+                const T* row = xp + static_cast<int64_t>(h + g.pH - kh) * g.W + w + g.pW;
+                for (int kw = 0; kw < g.kW; kw++)
                 {
-                    if (w0 + j >= g.W) continue;
-                    const int ch = winner[o][rr][j];
-                    const T* xp = xb + static_cast<int64_t>(ch) * plane;
-                    const T* wk = wo + ch * g.taps();
-                    T best = op_init;
-                    int arg = 0;
-                    for (int kh = 0; kh < g.kH; kh++)
-                        for (int kw = 0; kw < g.kW; kw++)
-                        {
-                            const T xv = read_border(xp, g, h + g.pH - kh, w0 + j + g.pW - kw, a.fill);
-                            const T wv = __ldg(wk + kh * g.kW + kw);
-                            const T v = IS_MIN ? xv - wv : xv + wv;
-                            if (strictly_better<IS_MIN>(v, best))
-                            {
-                                best = v;
-                                arg = kh * g.kW + kw;
-                            }
-                        }
-                    a.idx[row + w0 + j] = (ch << 16) | arg;
+                    const T wv = __ldg(wk + kh * g.kW + kw);
+                    const T xv = __ldg(row - kw);
+                    const T v = IS_MIN ? xv - wv : xv + wv;
+                    if (strictly_better<IS_MIN>(v, best))
+                    {
+                        best = v;
+                        arg = kh * g.kW + kw;
+                    }
                 }
             }
         }
+        else
+        {
+            for (int kh = 0; kh < g.kH; kh++)
+                for (int kw = 0; kw < g.kW; kw++)
+                {
+                    const T xv = read_border(xp, g, h + g.pH - kh, w + g.pW - kw, a.fill);
+                    const T wv = __ldg(wk + kh * g.kW + kw);
+                    const T v = IS_MIN ? xv - wv : xv + wv;
+                    if (strictly_better<IS_MIN>(v, best))
+                    {
+                        best = v;
+                        arg = kh * g.kW + kw;
+                    }
+                }
+        }
+        a.idx[at] = (ch << 16) | arg;
     }
 }
 
@@ -398,21 +436,30 @@ int launch_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx,
     // TMA staging when the tensor can be described by a tensor map (16-byte row pitch and base).
     ForwardPlan<T> plan;
     CUtensorMap tmap{};
+    int rc;
     if (plan_forward<T>(g, OB, 2, plan)
         && make_window_tensor_map(&tmap, x, sizeof(T), d.B, d.Ci, d.H, d.W, g.win_stride, g.win_rows, plan.chunk))
     {
         a.chunk = plan.chunk;
-        return track ? launch_forward_variant<T, IS_MIN, KW, OB, true, true>(a, tmap, blocks, plan.smem, stream)
-                     : launch_forward_variant<T, IS_MIN, KW, OB, false, true>(a, tmap, blocks, plan.smem, stream);
+        rc = track ? launch_forward_variant<T, IS_MIN, KW, OB, true, true>(a, tmap, blocks, plan.smem, stream)
+                   : launch_forward_variant<T, IS_MIN, KW, OB, false, true>(a, tmap, blocks, plan.smem, stream);
     }
-    if (!plan_forward<T>(g, OB, 1, plan))
+    else
     {
-        set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
-        return MC_ERR_UNSUPPORTED;
+        if (!plan_forward<T>(g, OB, 1, plan))
+        {
+            set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
+            return MC_ERR_UNSUPPORTED;
+        }
+        a.chunk = plan.chunk;
+        rc = track ? launch_forward_variant<T, IS_MIN, KW, OB, true, false>(a, tmap, blocks, plan.smem, stream)
+                   : launch_forward_variant<T, IS_MIN, KW, OB, false, false>(a, tmap, blocks, plan.smem, stream);
     }
-    a.chunk = plan.chunk;
-    return track ? launch_forward_variant<T, IS_MIN, KW, OB, true, false>(a, tmap, blocks, plan.smem, stream)
-                 : launch_forward_variant<T, IS_MIN, KW, OB, false, false>(a, tmap, blocks, plan.smem, stream);
+    if (rc != MC_OK || !track) return rc;
+    const int64_t total = static_cast<int64_t>(d.B) * d.Co * d.H * d.W;
+    const int64_t finder_blocks = std::min<int64_t>((total + THREADS - 1) / THREADS, 148LL * 64);
+    morpho_find_tap_kernel<T, IS_MIN><<<static_cast<unsigned>(finder_blocks), THREADS, 0, stream>>>(a, total);
+    return check_launch("morpho_find_tap_kernel");
 }
 
 }  // namespace mc

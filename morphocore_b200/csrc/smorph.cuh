@@ -6,14 +6,16 @@
 //     e_k = exp(alpha (v_k - ref)),  S = sum e_k,  out = (sum e_k v_k) / S
 // (reference: morphocore/functional/csrc/cpp/smorph_cpu_kernels.hxx:14-24, 76-147; CUDA kernels
 // csrc/cuda/smorph_kernels.cuh:80-175, 307-407, 418-571). The kernels work on u = s v with s = sign(alpha),
-// so both cases are a max and alpha (v_k - ref) = |alpha| (u_k - ref_u) <= 0: a pair with alpha >= 0 reads the
-// window of x and the structuring element w, a pair with alpha < 0 the window of -x and -w, and
-// u_k = xs_k + ws_k is one add. Window elements outside the image hold -1e30 in both windows: they never
-// win the maximum and their exponential is exactly zero (the exponent scale is clamped to 1e-20 from
-// below so that this also holds for alpha = 0), so excluded taps cost no instruction.
+// so both cases are a max and alpha (v_k - ref) = |alpha| (u_k - ref_u) <= 0; u_k = s x_k + (s w_k) is one fused
+// multiply-add with the sign folded into the staged structuring element. Window elements outside the
+// image hold -1e30 in the window read by pairs with alpha >= 0 and +1e30 in the one read by pairs with
+// alpha < 0, so u = -1e30 there: it never wins the maximum and its exponential is exactly zero (the
+// exponent scale is clamped to 1e-20 from below so that this also holds for alpha = 0). Excluded taps
+// therefore cost no instruction.
 #pragma once
 #include "common.cuh"
 #include "morpho_backward.cuh"
+#include "tma.cuh"
 
 namespace mc
 {
@@ -87,9 +89,9 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
 }
 
 /// Soft extremum of one staged pair for the thread's patch, in the u domain: ref_u, 1 / S and out_u.
-/// `win` is the window of s x and `swk` the structuring element s w (element k at swk[k * wstride]).
+/// `win` is the window of x for the sign s and `swk` the structuring element s w (element k at swk[k * wstride]).
 template <int KH, int KW, typename T>
-__device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* __restrict__ swk, int wstride, T scale, const Geometry& g, int tx,
+__device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* __restrict__ swk, int wstride, T s, T scale, const Geometry& g, int tx,
                                             int ty, T (&ref)[PATCH_H][PATCH_W], T (&inv_sum)[PATCH_H][PATCH_W], T (&out)[PATCH_H][PATCH_W])
 {
     const int kwr = KW > 0 ? KW : g.kW;
@@ -98,7 +100,7 @@ __device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* 
 #pragma unroll
         for (int j = 0; j < PATCH_W; j++) ref[rr][j] = -Limits<T>::inf();
     for_each_tap<KH, KW>(win, g, tx, ty, [&](int kh, int kw, int rr, int j, T xv) {
-        ref[rr][j] = ext2<false>(ref[rr][j], xv + swk[(kh * kwr + kw) * wstride]);
+        ref[rr][j] = ext2<false>(ref[rr][j], fma(s, xv, swk[(kh * kwr + kw) * wstride]));
     });
 
     T sum[PATCH_H][PATCH_W], weighted[PATCH_H][PATCH_W];
@@ -111,7 +113,7 @@ __device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* 
             weighted[rr][j] = T(0);
         }
     for_each_tap<KH, KW>(win, g, tx, ty, [&](int kh, int kw, int rr, int j, T xv) {
-        const T u = xv + swk[(kh * kwr + kw) * wstride];
+        const T u = fma(s, xv, swk[(kh * kwr + kw) * wstride]);
         const T e = soft_exp(u - ref[rr][j], scale);
         sum[rr][j] += e;
         weighted[rr][j] = fma(e, u, weighted[rr][j]);
@@ -141,10 +143,10 @@ __device__ __forceinline__ T warp_sum(T v)
 // per tap forward, of which one ex2, so the forward pass runs at the rate of the special-function unit.
 // ---------------------------------------------------------------------------------------------------
 
-/// u_k = xs + ws for the 4 pixels of patch row rr, k = kh * 3 + kw.
+/// u_k = s x + (s w) for the 4 pixels of patch row rr, k = kh * 3 + kw.
 template <typename T>
-__device__ __forceinline__ void smorph3_values(const T* __restrict__ win, const T* __restrict__ swk, int wstride, const Geometry& g, int tx, int ty,
-                                               int rr, T (&u)[9][PATCH_W])
+__device__ __forceinline__ void smorph3_values(const T* __restrict__ win, const T* __restrict__ swk, int wstride, T s, const Geometry& g, int tx,
+                                               int ty, int rr, T (&u)[9][PATCH_W])
 {
     constexpr int LEN = segment_len(3, sizeof(T)), OFF = segment_offset(3, sizeof(T));
 #pragma unroll
@@ -157,7 +159,7 @@ __device__ __forceinline__ void smorph3_values(const T* __restrict__ win, const 
         {
             const T wv = swk[(kh * 3 + kw) * wstride];
 #pragma unroll
-            for (int j = 0; j < PATCH_W; j++) u[kh * 3 + kw][j] = seg[OFF + j + 2 - kw] + wv;
+            for (int j = 0; j < PATCH_W; j++) u[kh * 3 + kw][j] = fma(s, seg[OFF + j + 2 - kw], wv);
         }
     }
 }
@@ -190,7 +192,7 @@ __device__ __forceinline__ void smorph3_softmax(const T (&u)[9][PATCH_W], T scal
 /// Backward of one 3 x 3 pair for the thread's patch, see smorph_pair_backward.
 template <typename T>
 __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ wbin, T* __restrict__ abin,
-                                                      T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W], const Geometry& g, int tx, int ty, int lane,
+                                                      T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W], const Geometry& g, int tx, int ty, int lane,
                                                       T (&gxr)[PATCH_H + 2][PATCH_W + 2])
 {
     T tap_sum[9];
@@ -201,7 +203,7 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
     for (int rr = 0; rr < PATCH_H; rr++)
     {
         T u[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out[PATCH_W];
-        smorph3_values(win, swk, 1, g, tx, ty, rr, u);
+        smorph3_values(win, swk, 1, s, g, tx, ty, rr, u);
         smorph3_softmax(u, scale, ref, e, inv_sum, out);
 #pragma unroll
         for (int j = 0; j < PATCH_W; j++)
@@ -242,21 +244,28 @@ struct SmorphForwardArgs
     int merge;
     int o_groups;
     int chunk;
+    unsigned int* errors;  // counter of timed-out waits
 };
 
-/// CTA = (batch element, group of OB output channels, tile), looping over chunks of input channels.
+/// CTA = (batch element, group of OB output channels, tile), looping over chunks of input channels; with
+/// USE_TMA the windows of chunk n + 1 are copied by TMA while chunk n is computed, see morpho_forward_kernel.
 /// STATS: instead of the merged output, count for MAX / MIN merges the channels whose soft extremum is
 /// within 1e-6 of the merged value, which share the gradient (csrc/cpp/smorph_cpu_kernels.hxx:397-398, 507-519).
-template <typename T, int KW, int OB, bool STATS>
-__global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forward_kernel(const SmorphForwardArgs<T> a)
+template <typename T, int KW, int OB, bool STATS, bool USE_TMA>
+__global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
+    smorph_forward_kernel(const SmorphForwardArgs<T> a, const __grid_constant__ CUtensorMap tmap)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const Geometry& g = a.g;
     const int taps = g.taps();
     const int welems = g.window_elems();
-    T* sx = reinterpret_cast<T*>(smem_raw);   // [chunk][2][window]: x and -x
-    T* sw = sx + a.chunk * 2 * welems;         // [chunk][taps][OB], sign folded
-    T* sa = sw + a.chunk * taps * OB;          // [chunk][OB][2]: sign, exp scale
+    // Layout: [2 mbarriers][pad to 128][stage 0][stage 1 (TMA only)][weights][signs and scales]; a stage is
+    // [slot][chunk][window]: slot 0 read by pairs of the CTA's first sign, slot 1 by the other sign if any.
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
+    const int slot_elems = (a.chunk * welems * static_cast<int>(sizeof(T)) + 127) / 128 * 128 / static_cast<int>(sizeof(T));
+    T* sx0 = reinterpret_cast<T*>(smem_raw + 128);
+    T* sw = sx0 + (USE_TMA ? 2 : 1) * 2 * slot_elems;   // [chunk][taps][OB], sign folded
+    T* sa = sw + a.chunk * taps * OB;                     // [chunk][OB][2]: sign, exp scale
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int og = blockIdx.x % a.o_groups;
@@ -271,6 +280,44 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
     const T* xb = a.x + static_cast<int64_t>(b) * g.Ci * plane;
     const int channels = g.identity ? 1 : g.Ci;
     const int wci = g.identity ? 1 : g.Ci;
+    const int first_channel = g.identity ? o0 : 0;
+
+    // Signs of every pair of this CTA: a single sign needs one window per channel, both signs need two.
+    bool any_pos = false, any_neg = false;
+    for (int e = threadIdx.x; e < channels * OB; e += THREADS)
+    {
+        const int o = e % OB, c = e / OB;
+        if (o0 + o >= g.Co) continue;
+        const T al = __ldg(a.alpha + (g.identity ? o0 + o : static_cast<int64_t>(o0 + o) * g.Ci + c));
+        any_pos |= al >= T(0);
+        any_neg |= al < T(0);
+    }
+    if constexpr (USE_TMA)
+    {
+        if (threadIdx.x == 0)
+        {
+            mbar_init(full, 1);
+            mbar_init(full + 1, 1);
+            mbar_fence_init();
+        }
+    }
+    any_pos = __syncthreads_or(any_pos);
+    any_neg = __syncthreads_or(any_neg);
+    const bool mixed = any_pos && any_neg;
+    const T fill0 = any_pos ? -Limits<T>::big() : Limits<T>::big();   // slot 0 serves alpha >= 0 unless every alpha is negative
+    const uint32_t slot_bytes = static_cast<uint32_t>(a.chunk) * welems * sizeof(T);
+    const bool border = window_leaves_image(g, tile_h0, tile_w0);
+    auto issue = [&](int n) {
+        uint64_t* bar = full + (n & 1);
+        T* stage = sx0 + (n & 1) * 2 * slot_elems;
+        mbar_expect_tx(bar, mixed ? 2 * slot_bytes : slot_bytes);
+        tma_load_4d(stage, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), first_channel + n * a.chunk, b);
+        if (mixed) tma_load_4d(stage + slot_elems, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), first_channel + n * a.chunk, b);
+    };
+    if constexpr (USE_TMA)
+    {
+        if (threadIdx.x == 0) issue(0);
+    }
 
     T merged[OB][PATCH_H][PATCH_W];
     T target[OB][PATCH_H][PATCH_W];
@@ -290,11 +337,29 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
                 }
             }
 
-    for (int c0 = 0; c0 < channels; c0 += a.chunk)
+    int n = 0;
+    for (int c0 = 0; c0 < channels; c0 += a.chunk, n++)
     {
         const int cc = min(a.chunk, channels - c0);
+        T* stage = sx0 + (USE_TMA ? (n & 1) * 2 * slot_elems : 0);
         __syncthreads();
-        bool has_pos = false, has_neg = false;
+        if constexpr (USE_TMA)
+        {
+            if (threadIdx.x == 0 && c0 + a.chunk < channels)
+            {
+                fence_async_smem();
+                issue(n + 1);
+            }
+        }
+        else
+        {
+            for (int c = 0; c < cc; c++)
+            {
+                const T* src = xb + static_cast<int64_t>(first_channel + c0 + c) * plane;
+                load_window_signed(any_pos ? stage + c * welems : nullptr, any_neg ? stage + (mixed ? slot_elems : 0) + c * welems : nullptr, src, g,
+                                   tile_h0, tile_w0);
+            }
+        }
         for (int e = threadIdx.x; e < cc * OB; e += THREADS)
         {
             const int o = e % OB, c = e / OB;
@@ -302,8 +367,6 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             if (o0 + o < g.Co) al = __ldg(a.alpha + (g.identity ? o0 + o : static_cast<int64_t>(o0 + o) * g.Ci + c0 + c));
             sa[e * 2] = al >= T(0) ? T(1) : T(-1);
             sa[e * 2 + 1] = exp_scale(al >= T(0) ? al : -al);
-            has_pos |= al >= T(0);
-            has_neg |= al < T(0);
         }
         for (int e = threadIdx.x; e < cc * taps * OB; e += THREADS)
         {
@@ -317,14 +380,19 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             }
             sw[e] = al >= T(0) ? v : -v;
         }
-        // Only the windows some pair of this chunk reads are staged.
-        has_pos = __syncthreads_or(has_pos);
-        has_neg = __syncthreads_or(has_neg);
-        for (int c = 0; c < cc; c++)
+        if constexpr (USE_TMA)
         {
-            const int ci = g.identity ? o0 : c0 + c;
-            load_window_signed(has_pos ? sx + (2 * c) * welems : nullptr, has_neg ? sx + (2 * c + 1) * welems : nullptr,
-                               xb + static_cast<int64_t>(ci) * plane, g, tile_h0, tile_w0);
+            if (!mbar_wait(full + (n & 1), (n >> 1) & 1))
+            {
+                if (threadIdx.x == 0 && a.errors != nullptr) atomicAdd(a.errors, 1u);
+                return;  // every thread of the CTA waits on the same barrier and gives up together
+            }
+            if (border)
+            {
+                const T* src = xb + static_cast<int64_t>(first_channel + c0) * plane;
+                fix_window_border(stage, src, plane, cc, g, tile_h0, tile_w0, fill0);
+                if (mixed) fix_window_border(stage + slot_elems, src, plane, cc, g, tile_h0, tile_w0, Limits<T>::big());
+            }
         }
         __syncthreads();
 
@@ -334,7 +402,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             for (int o = 0; o < OB; o++)
             {
                 const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
-                const T* win = sx + (2 * c + (s < T(0) ? 1 : 0)) * welems;
+                const T* win = stage + ((mixed && s < T(0)) ? slot_elems : 0) + c * welems;
                 T out[PATCH_H][PATCH_W];
                 if (KW == 3 && g.kH == 3)
                 {
@@ -342,14 +410,14 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
                     for (int rr = 0; rr < PATCH_H; rr++)
                     {
                         T u[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W];
-                        smorph3_values(win, sw + c * taps * OB + o, OB, g, tx, ty, rr, u);
+                        smorph3_values(win, sw + c * taps * OB + o, OB, s, g, tx, ty, rr, u);
                         smorph3_softmax(u, scale, ref, e, inv_sum, out[rr]);
                     }
                 }
                 else
                 {
                     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
-                    smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, scale, g, tx, ty, ref, inv_sum, out);
+                    smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, s, scale, g, tx, ty, ref, inv_sum, out);
                 }
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
@@ -388,6 +456,19 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2) smorph_forwar
             }
 }
 
+template <typename T, int KW, int OB, bool STATS, bool USE_TMA>
+int launch_smorph_forward_variant(const SmorphForwardArgs<T>& a, const CUtensorMap& tmap, int64_t blocks, size_t smem, cudaStream_t stream)
+{
+    auto kernel = smorph_forward_kernel<T, KW, OB, STATS, USE_TMA>;
+    if (!allow_shared(kernel, smem))
+    {
+        set_last_error("cannot opt in to %zu bytes of shared memory", smem);
+        return MC_ERR_UNSUPPORTED;
+    }
+    kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a, tmap);
+    return check_launch("smorph_forward_kernel");
+}
+
 template <typename T, int KW, int OB>
 int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, T* y, const T* target, T* counts, cudaStream_t stream)
 {
@@ -396,23 +477,39 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     a.g.replicate = false;  // out-of-image taps are excluded, never read
     a.x = x; a.w = w; a.alpha = alpha; a.y = y; a.target = target; a.counts = counts; a.merge = d.merge;
     a.o_groups = (d.Co + OB - 1) / OB;
-    const size_t per_channel = (2 * static_cast<size_t>(a.g.window_elems()) + static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);
-    if (per_channel > MAX_SHARED_BYTES)
+    a.errors = device_error_counter();
+    const int channels = a.g.identity ? 1 : d.Ci;
+    const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * a.o_groups * d.B;
+    if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
+    // Per channel: two window slots (one per sign) per stage, the structuring elements, signs and scales.
+    const size_t window = static_cast<size_t>(a.g.window_elems()) * sizeof(T);
+    const size_t small = (static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);
+    auto plan = [&](int stages, int& chunk, size_t& smem) {
+        const size_t per_channel = stages * 2 * window + small, fixed = 128 + stages * 2 * 128;
+        if (per_channel + fixed > MAX_SHARED_BYTES) return false;
+        chunk = static_cast<int>((100 * 1024 - fixed) / per_channel);
+        chunk = std::max(1, std::min(std::min(chunk, 8), channels));
+        smem = fixed + per_channel * chunk;
+        return true;
+    };
+    const bool stats = counts != nullptr;
+    CUtensorMap tmap{};
+    int chunk = 1;
+    size_t smem = 0;
+    if (plan(2, chunk, smem) && make_window_tensor_map(&tmap, x, sizeof(T), d.B, d.Ci, d.H, d.W, a.g.win_stride, a.g.win_rows, chunk))
+    {
+        a.chunk = chunk;
+        return stats ? launch_smorph_forward_variant<T, KW, OB, true, true>(a, tmap, blocks, smem, stream)
+                     : launch_smorph_forward_variant<T, KW, OB, false, true>(a, tmap, blocks, smem, stream);
+    }
+    if (!plan(1, chunk, smem))
     {
         set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
         return MC_ERR_UNSUPPORTED;
     }
-    const int channels = a.g.identity ? 1 : d.Ci;
-    int chunk = static_cast<int>((96 * 1024) / per_channel);
-    chunk = chunk < 1 ? 1 : (chunk > 8 ? 8 : chunk);
-    a.chunk = chunk > channels ? channels : chunk;
-    const size_t smem = per_channel * a.chunk;
-    const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * a.o_groups * d.B;
-    if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
-    auto kernel = counts != nullptr ? smorph_forward_kernel<T, KW, OB, true> : smorph_forward_kernel<T, KW, OB, false>;
-    if (!allow_shared(kernel, smem)) { set_last_error("cannot opt in to %zu bytes of shared memory", smem); return MC_ERR_UNSUPPORTED; }
-    kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a);
-    return check_launch("smorph_forward_kernel");
+    a.chunk = chunk;
+    return stats ? launch_smorph_forward_variant<T, KW, OB, true, false>(a, tmap, blocks, smem, stream)
+                 : launch_smorph_forward_variant<T, KW, OB, false, false>(a, tmap, blocks, smem, stream);
 }
 
 template <typename T>
@@ -446,12 +543,12 @@ struct SmorphBackwardArgs
 /// total in the warp's private bins (no atomics, no barrier).
 template <int KH, int KW, typename T, int GH, int GW>
 __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ sg, T* __restrict__ wbin,
-                                                     T* __restrict__ abin, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
+                                                     T* __restrict__ abin, T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
                                                      const Geometry& g, int tx, int ty, int lane, T (&gxr)[GH][GW])
 {
     const int kwr = KW > 0 ? KW : g.kW;
     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
-    smorph_pair<0, KW>(win, swk, 1, scale, g, tx, ty, ref, inv_sum, out);  // kernel rows not unrolled: smaller code, fewer live registers
+    smorph_pair<0, KW>(win, swk, 1, s, scale, g, tx, ty, ref, inv_sum, out);  // kernel rows not unrolled: smaller code, fewer live registers
 
     T scaled[PATCH_H][PATCH_W];
 #pragma unroll
@@ -473,7 +570,7 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
             if (current >= 0) flush_tap(current);
             current = k;
         }
-        const T u = xv + swk[k];
+        const T u = fma(s, xv, swk[k]);
         const T d = u - ref[rr][j];
         const T pg = soft_exp(d, scale) * scaled[rr][j];
         const T centered = u - out[rr][j];
@@ -501,7 +598,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     const int taps = g.taps();
     const int welems = g.window_elems();
     const int OC = a.o_chunk;
-    T* sx = reinterpret_cast<T*>(smem_raw);   // [2][window]: x and -x
+    T* sx = reinterpret_cast<T*>(smem_raw);   // [2][window]: x with -big / +big outside the image
     T* sg = sx + 2 * welems;                   // gradient window
     T* sw = sg + welems;                       // [OC][taps], sign folded
     T* spar = sw + OC * taps;                  // [OC][3]: sign, |alpha|, exp scale
@@ -600,7 +697,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                     // MAX / MIN: only the channels within 1e-6 of the merged value receive gradient, shared
                     // equally; the pair's own soft extremum is needed first.
                     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
-                    smorph_pair<0, KW>(win, sw + oo * taps, 1, scale, g, tx, ty, ref, inv_sum, out);
+                    smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -613,8 +710,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
                         }
                 }
-                if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
-                else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
