@@ -207,10 +207,10 @@ template <bool IS_MIN> __device__ __forceinline__ double ext2(double a, double b
 /// Three-input max / min: one sm_100 instruction for two taps.
 template <bool IS_MIN> __device__ __forceinline__ float ext3(float a, float b, float c)
 {
-    float d;
-    if (IS_MIN) asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    else asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
+    // The accumulator is a read-write operand so that the result stays in its register (no move per use).
+    if (IS_MIN) asm("min.f32 %0, %0, %1, %2;" : "+f"(a) : "f"(b), "f"(c));
+    else asm("max.f32 %0, %0, %1, %2;" : "+f"(a) : "f"(b), "f"(c));
+    return a;
 }
 template <bool IS_MIN> __device__ __forceinline__ double ext3(double a, double b, double c) { return ext2<IS_MIN>(ext2<IS_MIN>(a, b), c); }
 

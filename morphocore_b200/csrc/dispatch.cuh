@@ -5,11 +5,12 @@
 namespace mc
 {
 
-/// Call f(std::integral_constant<int, KW>) with the compiled kernel width matching kw, or 0 (any size).
+/// Call f(std::integral_constant<int, K>) with the compiled size of a square K x K structuring element
+/// (3, 5, 7 or 11), or 0 for any other shape, which takes the any-size path.
 template <typename F>
-inline int dispatch_kernel_width(int kw, F f)
+inline int dispatch_kernel_width(int kh, int kw, F f)
 {
-    switch (kw)
+    switch (kh == kw ? kw : 0)
     {
         case 3: return f(std::integral_constant<int, 3>{});
         case 5: return f(std::integral_constant<int, 5>{});

@@ -213,13 +213,13 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
 
             if constexpr (KW > 0)
             {
-                constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T));
-                for (int kh = 0; kh < g.kH; kh++)
+                constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T)), STRIDE = window_stride(KW, sizeof(T));
+                for (int kh = 0; kh < KW; kh++)
                 {
                     T seg[PATCH_H][LEN];
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
-                        load_segment<LEN>(seg[rr], sx + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W);
+                        load_segment<LEN>(seg[rr], sx + (ty * PATCH_H + rr + KW - 1 - kh) * STRIDE + tx * PATCH_W);
 #pragma unroll
                     for (int kw = 0; kw < KW; kw++)
                     {

@@ -34,7 +34,7 @@ int morpho_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const 
         return launch_backward_index<T>(d, idx, gy, gx, gw, stream);
     }
     const int ob = output_block<T>(d);
-    return dispatch_kernel_width(d.kW, [&](auto kw) {
+    return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
         if (d.op == MC_OP_DILATION)
             return ob == 1 ? launch_backward_pairs<T, false, KW, 1>(d, x, w, gy, gx, gw, stream)

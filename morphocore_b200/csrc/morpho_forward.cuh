@@ -57,13 +57,17 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
 {
     if constexpr (KW > 0)
     {
+        // Square KW x KW structuring element: kernel rows fully unrolled up to 7 x 7 (constant offsets, no
+        // loop-carried register moves).
         constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T));
-        for (int kh = 0; kh < g.kH; kh++)
+        constexpr int STRIDE = window_stride(KW, sizeof(T));
+        const T* base = win + (ty * PATCH_H) * STRIDE + tx * PATCH_W;
+#pragma unroll(KW <= 7 ? KW : 1)
+        for (int kh = 0; kh < KW; kh++)
         {
             T seg[PATCH_H][LEN];
 #pragma unroll
-            for (int rr = 0; rr < PATCH_H; rr++)
-                load_segment<LEN>(seg[rr], win + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W);
+            for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], base + (rr + KW - 1 - kh) * STRIDE);
             const T* wrow = wk + kh * KW * OB;
 #pragma unroll
             for (int kw = 0; kw + 1 < KW; kw += 2)

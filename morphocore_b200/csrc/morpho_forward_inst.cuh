@@ -13,7 +13,7 @@ int morpho_forward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, MC_T* y
     using T = MC_T;
     constexpr int WIDE = sizeof(T) == 4 ? 4 : 2;
     const int ob = output_block<T>(d);
-    return dispatch_kernel_width(d.kW, [&](auto kw) {
+    return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
         if (d.op == MC_OP_DILATION)
             return ob == 1 ? launch_forward<T, false, KW, 1>(d, x, w, y, idx, stream) : launch_forward<T, false, KW, WIDE>(d, x, w, y, idx, stream);

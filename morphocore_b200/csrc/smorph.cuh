@@ -51,12 +51,13 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
 {
     if constexpr (KW > 0)
     {
-        constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T));
+        // KW > 0 means a square KW x KW structuring element.
+        constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T)), STRIDE = window_stride(KW, sizeof(T));
         auto row = [&](int kh, int top) {
             T seg[PATCH_H][LEN];
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++)
-                load_segment<LEN>(seg[rr], win + (ty * PATCH_H + rr + top - kh) * g.win_stride + tx * PATCH_W);
+                load_segment<LEN>(seg[rr], win + (ty * PATCH_H + rr + top - kh) * STRIDE + tx * PATCH_W);
 #pragma unroll
             for (int kw = 0; kw < KW; kw++)
 #pragma unroll
@@ -71,7 +72,8 @@ __device__ __forceinline__ void for_each_tap(const T* __restrict__ win, const Ge
         }
         else
         {
-            for (int kh = 0; kh < g.kH; kh++) row(kh, g.kH - 1);
+#pragma unroll 1
+            for (int kh = 0; kh < KW; kh++) row(kh, KW - 1);
         }
     }
     else
@@ -148,12 +150,12 @@ template <typename T>
 __device__ __forceinline__ void smorph3_values(const T* __restrict__ win, const T* __restrict__ swk, int wstride, T s, const Geometry& g, int tx,
                                                int ty, int rr, T (&u)[9][PATCH_W])
 {
-    constexpr int LEN = segment_len(3, sizeof(T)), OFF = segment_offset(3, sizeof(T));
+    constexpr int LEN = segment_len(3, sizeof(T)), OFF = segment_offset(3, sizeof(T)), STRIDE = window_stride(3, sizeof(T));
 #pragma unroll
     for (int kh = 0; kh < 3; kh++)
     {
         T seg[LEN];
-        load_segment<LEN>(seg, win + (ty * PATCH_H + rr + 2 - kh) * g.win_stride + tx * PATCH_W);
+        load_segment<LEN>(seg, win + (ty * PATCH_H + rr + 2 - kh) * STRIDE + tx * PATCH_W);
 #pragma unroll
         for (int kw = 0; kw < 3; kw++)
         {
@@ -404,7 +406,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
                 const T* win = stage + ((mixed && s < T(0)) ? slot_elems : 0) + c * welems;
                 T out[PATCH_H][PATCH_W];
-                if (KW == 3 && g.kH == 3)
+                if constexpr (KW == 3)
                 {
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)

@@ -14,7 +14,7 @@ int smorph_forward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const M
     // Stats mode (counts != nullptr) reads y as the merge target instead of writing it.
     const T* target = counts != nullptr ? y : nullptr;
     const bool wide = d.merge != MC_MERGE_IDENTITY && d.Co >= 2;
-    return dispatch_kernel_width(d.kW, [&](auto kw) {
+    return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
         return wide ? launch_smorph_forward<T, KW, 2>(d, x, w, alpha, y, target, counts, stream)
                     : launch_smorph_forward<T, KW, 1>(d, x, w, alpha, y, target, counts, stream);
@@ -53,7 +53,7 @@ int smorph_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const 
         if (d.kW == 5) return launch_smorph_backward<T, 5, 5>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
         if (d.kW == 7) return launch_smorph_backward<T, 7, 7>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
     }
-    return dispatch_kernel_width(d.kW, [&](auto kw) {
+    return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
         return launch_smorph_backward<T, 0, KW>(d, x, w, alpha, y, counts, gy, gx, gw, galpha, stream);
     });
