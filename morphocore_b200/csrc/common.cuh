@@ -202,7 +202,10 @@ __device__ __forceinline__ void load_segment(T (&dst)[LEN], const T* src)
 // max / min with "the other operand when one is NaN" semantics, like the reference's strict
 // comparison from an initial value that is never NaN.
 template <bool IS_MIN> __device__ __forceinline__ float ext2(float a, float b) { return IS_MIN ? fminf(a, b) : fmaxf(a, b); }
-template <bool IS_MIN> __device__ __forceinline__ double ext2(double a, double b) { return IS_MIN ? fmin(a, b) : fmax(a, b); }
+// double: compare + select is more than twice as fast as fmax / fmin on this part (DSETP + 2 SEL against a
+// multi-instruction NaN-aware sequence) and has the same result: b replaces a only when strictly better,
+// so a NaN in b never wins.
+template <bool IS_MIN> __device__ __forceinline__ double ext2(double a, double b) { return (IS_MIN ? b < a : b > a) ? b : a; }
 
 /// Three-input max / min: one sm_100 instruction for two taps.
 template <bool IS_MIN> __device__ __forceinline__ float ext3(float a, float b, float c)
