@@ -37,14 +37,33 @@ import workloads as WL  # noqa: E402
 METRIC = "fwd+bwd Gtaps/s"
 UNIT = "Gtaps/s"
 
-# Instruction-mix ceilings measured on this pool's B200 with register-only probe kernels (every operand
-# loop carried; wall clock, SM clock at its 1965 MHz maximum), in taps/s: profiles/microbench_b200.md.
-PEAK_GTAPS = {
-    "morph_f32": 27300.0,   # add.f32x2 + 3-input max: the best add+max mix found (2 add + max3: 18 900; add + max: 13 400)
-    "morph_f64": 5750.0,    # DADD + compare/select (DADD + fmax: 2 600)
-    "smorph_fwd_f32": 4633.0,   # one ex2 per tap (MUFU, 15.9 per clock per SM)
-    "smorph_bwd_f32": 2316.0,   # two ex2 per tap: forward state recomputed, then the per-tap weights
-}
+# Roofline denominators in Gtaps/s: instruction-mix ceilings of the CUDA cores, measured LIVE at the start of
+# the run by morphocore_b200/probe_rates (register-only kernels, every operand loop carried). The values
+# below are an earlier measurement on this pool's B200 (profiles/probe_rates_b200.md), used only when the
+# probe binary is missing. A dilation / erosion tap is one add and one max; the float peak is the best mix
+# found (packed add.f32x2 + 3-input max), the double peak DADD + compare/select; a smorph tap costs one ex2
+# forward and two backward (forward state recomputed, then the per-tap weights).
+PEAK_GTAPS = {"morph_f32": 27300.0, "morph_f64": 5750.0, "smorph_fwd_f32": 4633.0, "smorph_bwd_f32": 2316.0}
+PEAK_SOURCE = "earlier measurement on this pool (probe binary missing)"
+
+
+def measure_peaks():
+    """Run the instruction-rate probe on the current GPU and fill PEAK_GTAPS; returns the raw rates."""
+    global PEAK_SOURCE
+    exe = os.path.join(ROOT, "morphocore_b200", "probe_rates")
+    if not os.path.exists(exe):
+        return None
+    try:
+        out = subprocess.run([exe], capture_output=True, text=True, timeout=120).stdout.strip().splitlines()[-1]
+        r = json.loads(out)
+        PEAK_GTAPS["morph_f32"] = max(r["add_max_taps"], r["add_max3_taps"], r["add2_max3_taps"])
+        PEAK_GTAPS["morph_f64"] = max(r["f64_add_fmax_taps"], r["f64_add_select_taps"])
+        PEAK_GTAPS["smorph_fwd_f32"] = r["ex2_ops"]
+        PEAK_GTAPS["smorph_bwd_f32"] = r["ex2_ops"] / 2
+        PEAK_SOURCE = "of measured (instruction-rate probe run on this GPU at the start of this bench)"
+        return r
+    except (OSError, ValueError, KeyError, IndexError, subprocess.TimeoutExpired):
+        return None
 
 
 def measured_peaks():
@@ -251,7 +270,7 @@ def cfg5_roofline(model, x, device):
     hbm_peak, which = measured_peaks()
     return {
         "kernel": name, "share_of_step": t / total, "bound": "cuda_core", "achieved": taps / t / 1e6, "peak": peak, "unit": UNIT,
-        "frac": taps / t / 1e6 / peak, "peak_source": "of measured (instruction-mix probe on this pool's B200, see profiles/)",
+        "frac": taps / t / 1e6 / peak, "peak_source": PEAK_SOURCE,
         "hbm": {"bound": "hbm", "achieved": alg_bytes / t / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": alg_bytes / t / 1e6 / hbm_peak,
                 "peak_source": f"of {which}", "algorithmic_bytes_per_launch": alg_bytes},
         "traffic": load_traffic(name),
@@ -420,6 +439,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    probe = measure_peaks() if rank == 0 else None
     line = {"metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
     if args.workload == "cfg5":
@@ -438,6 +458,8 @@ def main():
             ms = statistics.mean(r["seconds"]) * 1e3
             line["cpu_baseline"] = {"value": r["n_taps"] / ms / 1e6, "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"],
                                     "ms_per_step": ms}
+        line["probe_gunits_per_s"] = probe
+        line["peaks_gtaps"] = dict(PEAK_GTAPS)
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

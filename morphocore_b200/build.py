@@ -80,9 +80,20 @@ def build_ext(force=False, verbose=False):
     return EXT
 
 
+def build_probe(force=False, verbose=False):
+    """The instruction-rate probe bench.py runs for its roofline denominators (a stand-alone executable)."""
+    src, out = os.path.join(CSRC, "probe_rates.cu"), os.path.join(PKG, "probe_rates")
+    if not force and _newer(out, [src]):
+        return out
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-o", out, src], check=True)
+    return out
+
+
 def build(force=False, verbose=False):
     build_cuda(force, verbose)
     build_ext(force, verbose)
+    build_probe(force, verbose)
 
 
 if __name__ == "__main__":

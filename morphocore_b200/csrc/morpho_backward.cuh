@@ -322,6 +322,13 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
     }
 }
 
+}  // namespace mc
+
+#include "morpho_backward_rows.cuh"
+
+namespace mc
+{
+
 template <typename T, bool IS_MIN, int KW, int OB>
 int launch_backward_pairs(const mc_desc& d, const T* x, const T* w, const T* gy, T* gx, T* gw, cudaStream_t stream)
 {
@@ -332,6 +339,21 @@ int launch_backward_pairs(const mc_desc& d, const T* x, const T* w, const T* gy,
     a.scale = d.merge == MC_MERGE_AVERAGE ? T(1.0) / static_cast<T>(d.Ci) : T(1.0);
     a.sign = d.op == MC_OP_DILATION ? T(1) : T(-1);
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
+    const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * d.Ci * d.B;
+    if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
+    if constexpr (sizeof(T) == 4 && (KW == 3 || KW == 5 || KW == 7))
+    {
+        const size_t bytes = pairs_rows_smem<KW>(a.g, a.g.identity ? 1 : d.Co);
+        if (bytes > 0)
+        {
+            auto fast = morpho_backward_pairs_rows_kernel<IS_MIN, KW>;
+            if (allow_shared(fast, bytes))
+            {
+                fast<<<static_cast<unsigned>(blocks), THREADS, bytes, stream>>>(a);
+                return check_launch("morpho_backward_pairs_rows_kernel");
+            }
+        }
+    }
     const size_t fixed = (2 * static_cast<size_t>(a.g.window_elems()) + (taps * OB + 3) / 4 * 4) * sizeof(T);
     if (fixed + taps * OB * sizeof(T) > MAX_SHARED_BYTES)
     {
@@ -341,8 +363,6 @@ int launch_backward_pairs(const mc_desc& d, const T* x, const T* w, const T* gy,
     a.copies = bin_copies(taps * OB, sizeof(T), std::min<size_t>(32 * 1024, MAX_SHARED_BYTES - fixed));
     if (a.copies < 1) a.copies = 1;
     const size_t smem = fixed + taps * OB * a.copies * sizeof(T);
-    const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * d.Ci * d.B;
-    if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
     auto kernel = morpho_backward_pairs_kernel<T, IS_MIN, KW, OB>;
     if (!allow_shared(kernel, smem)) { set_last_error("cannot opt in to %zu bytes of shared memory", smem); return MC_ERR_UNSUPPORTED; }
     kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a);
