@@ -251,30 +251,27 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
             window_extremum<T, IS_MIN, KW, OB>(acc, sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
 
             const int ci = c0 + c;
+            // The merge mode is the same for every pixel: one switch around the pixel loops.
+            auto for_values = [&](auto f) {
 #pragma unroll
-            for (int o = 0; o < OB; o++)
+                for (int o = 0; o < OB; o++)
 #pragma unroll
-                for (int rr = 0; rr < PATCH_H; rr++)
+                    for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++)
-                    {
-                        const T v = acc[o][rr][j];
-                        T& m = merged[o][rr][j];
-                        if (a.merge == MC_MERGE_MAX)
-                        {
-                            if constexpr (TRACK)
-                                if (ci == 0 || v > m) winner[o][rr][j] = ci;
-                            m = m < v ? v : m;
-                        }
-                        else if (a.merge == MC_MERGE_MIN)
-                        {
-                            if constexpr (TRACK)
-                                if (ci == 0 || v < m) winner[o][rr][j] = ci;
-                            m = v < m ? v : m;
-                        }
-                        else if (a.merge == MC_MERGE_IDENTITY) m = v;
-                        else m = m + v;
-                    }
+                        for (int j = 0; j < PATCH_W; j++) f(merged[o][rr][j], acc[o][rr][j], winner[TRACK ? o : 0][rr][j]);
+            };
+            if (a.merge == MC_MERGE_MAX)
+                for_values([&](T& m, T v, int& win) {
+                    if (TRACK && (ci == 0 || v > m)) win = ci;
+                    m = m < v ? v : m;
+                });
+            else if (a.merge == MC_MERGE_MIN)
+                for_values([&](T& m, T v, int& win) {
+                    if (TRACK && (ci == 0 || v < m)) win = ci;
+                    m = v < m ? v : m;
+                });
+            else if (a.merge == MC_MERGE_IDENTITY) for_values([](T& m, T v, int&) { m = v; });
+            else for_values([](T& m, T v, int&) { m = m + v; });
         }
     }
 

@@ -166,36 +166,46 @@ __device__ __forceinline__ void smorph3_values(const T* __restrict__ win, const 
     }
 }
 
-/// ref, e_k, 1 / S and out_u of 4 pixels from their u_k.
+/// From the u_k of 4 pixels: ref = max_k u_k, then IN PLACE d_k = u_k - ref, and e_k = exp(|alpha| d_k),
+/// 1 / S and out_d = sum_k e_k d_k / S, the soft extremum relative to ref (out_u = ref + out_d).
 template <typename T>
-__device__ __forceinline__ void smorph3_softmax(const T (&u)[9][PATCH_W], T scale, T (&ref)[PATCH_W], T (&e)[9][PATCH_W], T (&inv_sum)[PATCH_W],
-                                                T (&out)[PATCH_W])
+__device__ __forceinline__ void smorph3_softmax(T (&d)[9][PATCH_W], T scale, T (&ref)[PATCH_W], T (&e)[9][PATCH_W], T (&inv_sum)[PATCH_W],
+                                                T (&out_d)[PATCH_W])
 {
 #pragma unroll
     for (int j = 0; j < PATCH_W; j++)
     {
-        T m = ext3<false>(u[0][j], u[1][j], u[2][j]);
-        m = ext3<false>(m, u[3][j], u[4][j]);
-        m = ext3<false>(m, u[5][j], u[6][j]);
-        ref[j] = ext3<false>(m, u[7][j], u[8][j]);
+        T m = ext3<false>(d[0][j], d[1][j], d[2][j]);
+        m = ext3<false>(m, d[3][j], d[4][j]);
+        m = ext3<false>(m, d[5][j], d[6][j]);
+        ref[j] = ext3<false>(m, d[7][j], d[8][j]);
         T sum = T(0), weighted = T(0);
 #pragma unroll
         for (int k = 0; k < 9; k++)
         {
-            e[k][j] = soft_exp(u[k][j] - ref[j], scale);
+            d[k][j] -= ref[j];
+            e[k][j] = soft_exp(d[k][j], scale);
             sum += e[k][j];
-            weighted = fma(e[k][j], u[k][j], weighted);
+            weighted = fma(e[k][j], d[k][j], weighted);
         }
         inv_sum[j] = soft_rcp(sum);
-        out[j] = weighted * inv_sum[j];
+        out_d[j] = weighted * inv_sum[j];
     }
 }
 
-/// Backward of one 3 x 3 pair for the thread's patch, see smorph_pair_backward.
+/// Rows of the per-warp scratch used to add 10 per-lane values over the warp (33 floats per row: the odd
+/// stride keeps both the writes and the strip reads free of bank conflicts).
+constexpr int RED_ROWS = 10, RED_STRIDE = 33;
+
+/// Backward of one 3 x 3 pair for the thread's patch, see smorph_pair_backward. With d_k = u_k - ref and
+/// out_d = out_u - ref: p_k g = e_k (g / S), pc_k = p_k g (d_k - out_d), c_k = p_k g + |alpha| pc_k and the
+/// alpha gradient is sum_k pc_k d_k. The 9 tap sums and the alpha sum of the 32 lanes are added through the
+/// warp's scratch `red`: every lane stores its 10 values, three lanes per row add a strip of 11 columns
+/// each, two shuffles join the strips.
 template <typename T>
 __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ wbin, T* __restrict__ abin,
-                                                      T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W], const Geometry& g, int tx, int ty, int lane,
-                                                      T (&gxr)[PATCH_H + 2][PATCH_W + 2])
+                                                      T* __restrict__ red, T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
+                                                      const Geometry& g, int tx, int ty, int lane, T (&gxr)[PATCH_H + 2][PATCH_W + 2])
 {
     T tap_sum[9];
 #pragma unroll
@@ -204,9 +214,9 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
     {
-        T u[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out[PATCH_W];
-        smorph3_values(win, swk, 1, s, g, tx, ty, rr, u);
-        smorph3_softmax(u, scale, ref, e, inv_sum, out);
+        T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+        smorph3_values(win, swk, 1, s, g, tx, ty, rr, d);
+        smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
 #pragma unroll
         for (int j = 0; j < PATCH_W; j++)
         {
@@ -215,22 +225,34 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
             for (int k = 0; k < 9; k++)
             {
                 const T pg = e[k][j] * scaled;
-                const T centered = u[k][j] - out[j];
-                const T c = fma(abs_alpha * pg, centered, pg);
+                const T pc = pg * (d[k][j] - out_d[j]);
+                const T c = fma(abs_alpha, pc, pg);
                 gxr[rr + 2 - k / 3][j + 2 - k % 3] += c;
                 tap_sum[k] += c;
-                alpha_sum = fma(pg * (u[k][j] - ref[j]), centered, alpha_sum);
+                alpha_sum = fma(pc, d[k][j], alpha_sum);
             }
         }
     }
+    __syncwarp();
 #pragma unroll
-    for (int k = 0; k < 9; k++)
+    for (int k = 0; k < 9; k++) red[k * RED_STRIDE + lane] = tap_sum[k];
+    red[9 * RED_STRIDE + lane] = alpha_sum;
+    __syncwarp();
+    T part = T(0);
+    if (lane < 3 * RED_ROWS)
     {
-        const T total = warp_sum(tap_sum[k]);
-        if (lane == 0) wbin[k] = total;
+        const T* strip = red + (lane / 3) * RED_STRIDE + (lane % 3) * 11;
+        const int n = (lane % 3) == 2 ? 10 : 11;
+#pragma unroll
+        for (int c = 0; c < 11; c++)
+            if (c < n) part += strip[c];
     }
-    alpha_sum = warp_sum(alpha_sum);
-    if (lane == 0) *abin = alpha_sum;
+    part += __shfl_down_sync(0xffffffffu, part, 1) + __shfl_down_sync(0xffffffffu, part, 2);
+    if (lane < 3 * RED_ROWS && lane % 3 == 0)
+    {
+        if (lane < 27) wbin[lane / 3] = part;
+        else *abin = part;
+    }
 }
 
 template <typename T>
@@ -411,9 +433,11 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
                     {
-                        T u[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W];
-                        smorph3_values(win, sw + c * taps * OB + o, OB, s, g, tx, ty, rr, u);
-                        smorph3_softmax(u, scale, ref, e, inv_sum, out[rr]);
+                        T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+                        smorph3_values(win, sw + c * taps * OB + o, OB, s, g, tx, ty, rr, d);
+                        smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+#pragma unroll
+                        for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
                     }
                 }
                 else
@@ -421,23 +445,22 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
                     smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, s, scale, g, tx, ty, ref, inv_sum, out);
                 }
+                // The merge mode is the same for every pixel: one switch around the pixel loops.
+                auto for_pixels = [&](auto f) {
 #pragma unroll
-                for (int rr = 0; rr < PATCH_H; rr++)
+                    for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++)
-                    {
-                        const T v = s * out[rr][j];
-                        T& m = merged[o][rr][j];
-                        if constexpr (STATS)
-                        {
-                            const T dist = v - target[o][rr][j];
-                            if (dist < T(1e-6) && dist > -T(1e-6)) m += T(1);
-                        }
-                        else if (a.merge == MC_MERGE_MAX) m = m < v ? v : m;
-                        else if (a.merge == MC_MERGE_MIN) m = v < m ? v : m;
-                        else if (a.merge == MC_MERGE_IDENTITY) m = v;
-                        else m = m + v;
-                    }
+                        for (int j = 0; j < PATCH_W; j++) f(merged[o][rr][j], s * out[rr][j], target[o][rr][j]);
+                };
+                if constexpr (STATS)
+                    for_pixels([](T& m, T v, T t) {
+                        const T dist = v - t;
+                        if (dist < T(1e-6) && dist > -T(1e-6)) m += T(1);
+                    });
+                else if (a.merge == MC_MERGE_MAX) for_pixels([](T& m, T v, T) { m = m < v ? v : m; });
+                else if (a.merge == MC_MERGE_MIN) for_pixels([](T& m, T v, T) { m = v < m ? v : m; });
+                else if (a.merge == MC_MERGE_IDENTITY) for_pixels([](T& m, T v, T) { m = v; });
+                else for_pixels([](T& m, T v, T) { m = m + v; });
             }
         }
     }
@@ -606,6 +629,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     T* spar = sw + OC * taps;                  // [OC][3]: sign, |alpha|, exp scale
     T* wbins = spar + OC * 3;                  // [WARPS][OC][taps]
     T* abins = wbins + WARPS * OC * taps;      // [WARPS][OC]
+    T* red = abins + WARPS * OC + (threadIdx.x >> 5) * RED_ROWS * RED_STRIDE;  // this warp's reduction scratch
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int ci = blockIdx.x % g.Ci;
@@ -712,7 +736,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
                         }
                 }
-                if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
                 else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
@@ -777,7 +801,7 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     a.merge = d.merge;
     a.scale = d.merge == MC_MERGE_AVERAGE ? T(1.0) / static_cast<T>(d.Ci) : T(1.0);
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
-    const size_t fixed = 3 * static_cast<size_t>(a.g.window_elems()) * sizeof(T);
+    const size_t fixed = (3 * static_cast<size_t>(a.g.window_elems()) + WARPS * RED_ROWS * RED_STRIDE) * sizeof(T);
     const size_t per_o = (taps + 3 + WARPS * (taps + 1)) * sizeof(T);
     if (fixed + per_o > MAX_SHARED_BYTES)
     {

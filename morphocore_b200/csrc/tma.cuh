@@ -101,6 +101,10 @@ __device__ __forceinline__ void fix_window_border(T* __restrict__ win, const T* 
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
+    // Columns [0, n_left) and [first_right, stride) of a row inside the image lie outside it.
+    const int n_left = min(max(-col0, 0), g.win_stride);
+    const int first_right = min(max(g.W - col0, 0), g.win_stride);
+    const int n_side = n_left + g.win_stride - first_right;
     for (int r = warp; r < g.win_rows * channels; r += THREADS / 32)
     {
         const int c = r / g.win_rows, wr = r % g.win_rows;
@@ -108,11 +112,11 @@ __device__ __forceinline__ void fix_window_border(T* __restrict__ win, const T* 
         const bool row_in = iy >= 0 && iy < g.H;
         const T* src = planes + c * plane_stride + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W;
         T* out = win + static_cast<int64_t>(c) * g.window_elems() + wr * g.win_stride;
-        for (int col = lane; col < g.win_stride; col += 32)
+        const int count = row_in ? n_side : g.win_stride;
+        for (int e = lane; e < count; e += 32)
         {
-            const int ix = col0 + col;
-            if (row_in && ix >= 0 && ix < g.W) continue;
-            out[col] = g.replicate ? __ldg(src + min(max(ix, 0), g.W - 1)) : outside;
+            const int col = (!row_in || e < n_left) ? e : first_right + e - n_left;
+            out[col] = g.replicate ? __ldg(src + min(max(col0 + col, 0), g.W - 1)) : outside;
         }
     }
 }
