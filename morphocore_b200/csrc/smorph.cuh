@@ -722,8 +722,25 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                 {
                     // MAX / MIN: only the channels within 1e-6 of the merged value receive gradient, shared
                     // equally; the pair's own soft extremum is needed first.
-                    T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
-                    smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
+                    // Same arithmetic as the forward kernel, so that the winning channel reproduces y exactly.
+                    T out[PATCH_H][PATCH_W];
+                    if constexpr (KW == 3)
+                    {
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+                        {
+                            T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+                            smorph3_values(win, sw + oo * taps, 1, s, g, tx, ty, rr, d);
+                            smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+#pragma unroll
+                            for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
+                        }
+                    }
+                    else
+                    {
+                        T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
+                        smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
+                    }
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
