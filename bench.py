@@ -273,14 +273,15 @@ def cfg5_roofline(model, x, device):
         "frac": taps / t / 1e6 / peak, "peak_source": PEAK_SOURCE,
         "hbm": {"bound": "hbm", "achieved": alg_bytes / t / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": alg_bytes / t / 1e6 / hbm_peak,
                 "peak_source": f"of {which}", "algorithmic_bytes_per_launch": alg_bytes},
-        "traffic": load_traffic(name),
+        "traffic": load_traffic(name, taps),
         "layers_ms": {r[1]: round(r[0], 3) for r in rows}, "sample_batch": B,
     }
 
 
-def load_traffic(kernel_name):
-    """dram bytes read + written per launch from the committed ncu summary (profiles/traffic.json), scaled
-    by nothing: null when no capture of this kernel is recorded."""
+def load_traffic(kernel_name, taps):
+    """DRAM bytes read + written by one launch of the named kernel: the bytes per tap of the committed ncu
+    capture (profiles/traffic.json, a smaller batch of the same layer; traffic grows in proportion to the
+    batch) times the taps of this launch. null when no capture of this kernel is recorded."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     if not os.path.exists(path):
         return None
@@ -288,7 +289,7 @@ def load_traffic(kernel_name):
         table = json.load(f)
     for key, value in table.items():
         if key in kernel_name:
-            return value
+            return value["dram_bytes_per_tap"] * taps
     return None
 
 
@@ -410,6 +411,41 @@ def reference_arm(args):
     print(json.dumps(line))
 
 
+def run_case(name, batch, device):
+    """One operator of one configuration at a reduced batch, run twice (warm-up + the launch to capture
+    under ncu): the small cases behind the summaries in profiles/."""
+    import morphocore_b200.functional as F
+    part, direction = name.rsplit("_", 1)
+    if part == "cfg2":
+        c = WL.cfg2(B=batch)
+        args, fn = (c["x"], c["w"]), (lambda x, w: F.erosion(x, w, "sum"))
+    elif part == "cfg3":
+        c = WL.cfg3(2.0, B=batch)
+        args, fn = (c["x"], c["w"], c["alpha"]), (lambda x, w, a: F.smorph(x, w, a, channel_merge_mode="mean"))
+    elif part == "cfg4":
+        c = WL.cfg4("dilation", B=batch)
+        args, fn = (c["x"], c["w"]), (lambda x, w: F.dilation(x, w, "identity"))
+    elif part in ("cfg5l2", "cfg5l3"):
+        g = torch.Generator().manual_seed(0)
+        x = torch.rand((batch, 64, 224, 224), generator=g)
+        if part == "cfg5l2":
+            args = (x, 0.1 * torch.randn((64, 64, 3, 3), generator=g), torch.full((64, 64), 2.0))
+            fn = lambda x, w, a: F.smorph(x, w, a, channel_merge_mode="sum")
+        else:
+            args, fn = (x, 0.1 * torch.randn((64, 64, 5, 5), generator=g)), (lambda x, w: F.erosion(x, w, "max"))
+        c = {"gy": torch.randn((batch, 64, 224, 224), generator=g)}
+    else:
+        raise SystemExit(f"unknown case {name}")
+    args = [t.to(device).requires_grad_(direction == "bwd") for t in args]
+    gy = c["gy"].to(device)
+    for _ in range(2):
+        y = fn(*args)
+        if direction == "bwd":
+            y.backward(gy)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": name, "batch": batch, "done": True}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -421,6 +457,9 @@ def main():
     ap.add_argument("--ref-batch", type=int, default=2, help="images per step of the CPU reference sample")
     ap.add_argument("--no-configs", action="store_true", help="skip configurations 1-4")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--case", default=None, help="profiling helper: run one operator twice and exit, e.g. cfg2_fwd, cfg2_bwd, cfg3_fwd, "
+                    "cfg3_bwd, cfg4_fwd, cfg4_bwd, cfg5l2_fwd, cfg5l2_bwd, cfg5l3_fwd, cfg5l3_bwd (with --case-batch)")
+    ap.add_argument("--case-batch", type=int, default=4)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -439,6 +478,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    if args.case:
+        run_case(args.case, args.case_batch, device)
+        return
     probe = measure_peaks() if rank == 0 else None
     line = {"metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic"}

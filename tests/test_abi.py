@@ -29,7 +29,7 @@ def declared_functions():
 
 def test_header_declares_the_entry_points():
     names = declared_functions()
-    for expected in ("mc_morpho_forward", "mc_morpho_backward", "mc_smorph_forward", "mc_smorph_backward",
+    for expected in ("mc_morpho_forward", "mc_morpho_backward", "mc_smorph_forward", "mc_smorph_backward", "mc_device_error_count",
                      "mc_morpho_backward_workspace_bytes", "mc_smorph_backward_workspace_bytes", "mc_status_string"):
         assert expected in names
 
