@@ -170,3 +170,33 @@ def test_cfg5_training_step_matches_reference(golden):
         if hasattr(layer, "alpha"):
             want = data[f"cfg5_galpha{n}"]
             np.testing.assert_allclose(layer.alpha.grad.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * float(np.abs(want).max()))
+
+
+def test_compositions(F):
+    """opening / closing with one shared structuring element and geodesic padding are idempotent and
+    (anti-)extensive; sigma_layer blends erosion and dilation (the reference's
+    tests/functional/test_opening_closing_sharing.py:40-47)."""
+    import morphocore_b200.nn as Mnn
+    torch.manual_seed(3)
+    x = torch.randn(2, 3, 20, 24, device="cuda")
+    op, cl = Mnn.Opening(3, 3, 3, padding_mode="geodesic").cuda(), Mnn.Closing(3, 3, 3, padding_mode="geodesic").cuda()
+    assert op.dilation.weight is op.erosion.weight and len(list(op.parameters())) == 1
+    with torch.no_grad():
+        # a flat structuring element contains the origin, which makes the opening anti-extensive
+        y = op(x)
+        assert torch.equal(op(y), y) and (y <= x).all()
+        z = cl(x)
+        assert torch.equal(cl(z), z) and (z >= x).all()
+        op.erosion.weight.copy_(torch.randn(3, 1, 3, 3))
+        y = op(x)
+        torch.testing.assert_close(op(y), y, rtol=0, atol=1e-5)   # idempotent for any structuring element
+    w = torch.randn(4, 3, 3, 3, device="cuda")
+    a = torch.zeros(4, 3, device="cuda")
+    mid = F.sigma_layer(x, w, a)
+    torch.testing.assert_close(mid, 0.5 * (F.erosion(x, w) + F.dilation(x, w)))
+    assert torch.equal(F.opening(x, w, w[:, :1].contiguous()), F.dilation(F.erosion(x, w), w[:, :1].contiguous(), "identity"))
+    with pytest.raises(ValueError, match="share_weights"):
+        Mnn.Opening(3, 4, 3)
+    layer = Mnn.SigmaLayer(3, 4, 3).cuda()
+    layer(x).sum().backward()
+    assert layer.alpha.grad is not None and layer.weight.grad is not None
