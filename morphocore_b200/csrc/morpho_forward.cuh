@@ -18,6 +18,12 @@
 namespace mc
 {
 
+#ifndef MC_PACKED_ADD
+#define MC_PACKED_ADD 1
+#endif
+/// Use the packed add.f32x2 of sm_100 in the float tap loop.
+constexpr bool PACKED_ADD = MC_PACKED_ADD != 0;
+
 template <typename T>
 struct ForwardArgs
 {
@@ -51,7 +57,7 @@ __device__ __forceinline__ void load_weights(T (&dst)[OB], const T* src)
 }
 
 /// Extremum over the structuring element of one staged channel, for the thread's OB x 2 x 4 block.
-template <typename T, bool IS_MIN, int KW, int OB>
+template <typename T, bool IS_MIN, int KW, int OB, bool PACKED>
 __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], const T* __restrict__ win, const T* __restrict__ wk,
                                                 const Geometry& g, int tx, int ty)
 {
@@ -69,6 +75,65 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], base + (rr + KW - 1 - kh) * STRIDE);
             const T* wrow = wk + kh * KW * OB;
+            if constexpr (sizeof(T) == 4 && PACKED && PACKED_ADD)
+            {
+                // Packed adds (add.f32x2): two adjacent pixels per instruction. Pixel pairs start at segment
+                // element OFF + j + KW-1-kw (j = 0, 2); even starts are register pairs as loaded, odd starts
+                // come from a copy of the segment shifted by one element.
+                float2 even[PATCH_H][LEN / 2], odd[PATCH_H][LEN / 2];
+#pragma unroll
+                for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                    for (int i = 0; i < LEN / 2; i++)
+                    {
+                        even[rr][i] = make_float2(seg[rr][2 * i], seg[rr][2 * i + 1]);
+                        odd[rr][i] = make_float2(seg[rr][2 * i + 1], seg[rr][2 * i + 2 < LEN ? 2 * i + 2 : 2 * i + 1]);
+                    }
+                auto pair_at = [&](int rr, int start) { return (start & 1) ? odd[rr][start >> 1] : even[rr][start >> 1]; };
+#pragma unroll
+                for (int kw = 0; kw + 1 < KW; kw += 2)
+                {
+                    T w0[OB], w1[OB];
+                    load_weights<OB>(w0, wrow + kw * OB);
+                    load_weights<OB>(w1, wrow + (kw + 1) * OB);
+#pragma unroll
+                    for (int o = 0; o < OB; o++)
+                    {
+                        const float2 wa = make_float2(w0[o], w0[o]), wb = make_float2(w1[o], w1[o]);
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                            for (int j = 0; j < PATCH_W; j += 2)
+                            {
+                                const float2 va = __fadd2_rn(pair_at(rr, OFF + j + KW - 1 - kw), wa);
+                                const float2 vb = __fadd2_rn(pair_at(rr, OFF + j + KW - 2 - kw), wb);
+                                acc[o][rr][j] = ext3<IS_MIN>(acc[o][rr][j], va.x, vb.x);
+                                acc[o][rr][j + 1] = ext3<IS_MIN>(acc[o][rr][j + 1], va.y, vb.y);
+                            }
+                    }
+                }
+                if constexpr (KW & 1)
+                {
+                    T w0[OB];
+                    load_weights<OB>(w0, wrow + (KW - 1) * OB);
+#pragma unroll
+                    for (int o = 0; o < OB; o++)
+                    {
+                        const float2 wa = make_float2(w0[o], w0[o]);
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                            for (int j = 0; j < PATCH_W; j += 2)
+                            {
+                                const float2 va = __fadd2_rn(pair_at(rr, OFF + j), wa);
+                                acc[o][rr][j] = ext2<IS_MIN>(acc[o][rr][j], va.x);
+                                acc[o][rr][j + 1] = ext2<IS_MIN>(acc[o][rr][j + 1], va.y);
+                            }
+                    }
+                }
+            }
+            else
+            {
 #pragma unroll
             for (int kw = 0; kw + 1 < KW; kw += 2)
             {
@@ -93,6 +158,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
                         for (int j = 0; j < PATCH_W; j++) acc[o][rr][j] = ext2<IS_MIN>(acc[o][rr][j], seg[rr][OFF + j] + w0[o]);
+            }
             }
         }
     }
@@ -248,7 +314,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
 #pragma unroll
                     for (int j = 0; j < PATCH_W; j++) acc[o][rr][j] = op_init;
 
-            window_extremum<T, IS_MIN, KW, OB>(acc, sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
+            window_extremum<T, IS_MIN, KW, OB, !TRACK>(acc,  // the index-tracking variant has no registers to spare for the pair copies
+                                                            sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
 
             const int ci = c0 + c;
             // The merge mode is the same for every pixel: one switch around the pixel loops.

@@ -288,8 +288,8 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
     const int slot_elems = (a.chunk * welems * static_cast<int>(sizeof(T)) + 127) / 128 * 128 / static_cast<int>(sizeof(T));
     T* sx0 = reinterpret_cast<T*>(smem_raw + 128);
-    T* sw = sx0 + (USE_TMA ? 2 : 1) * 2 * slot_elems;   // [chunk][taps][OB], sign folded
-    T* sa = sw + a.chunk * taps * OB;                     // [chunk][OB][2]: sign, exp scale
+    T* sw = sx0 + (USE_TMA ? 2 : 1) * 2 * slot_elems;   // [2 chunk][taps][OB], sign folded
+    T* sa = sw + 2 * a.chunk * taps * OB;                 // [2 chunk][OB][2]: sign, exp scale
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int og = blockIdx.x % a.o_groups;
@@ -328,15 +328,21 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     any_pos = __syncthreads_or(any_pos);
     any_neg = __syncthreads_or(any_neg);
     const bool mixed = any_pos && any_neg;
+    // Channels per stage: with a single sign both slots of a stage hold channels, twice as many per barrier.
+    const int span = mixed ? a.chunk : 2 * a.chunk;
     const T fill0 = any_pos ? -Limits<T>::big() : Limits<T>::big();   // slot 0 serves alpha >= 0 unless every alpha is negative
     const uint32_t slot_bytes = static_cast<uint32_t>(a.chunk) * welems * sizeof(T);
     const bool border = window_leaves_image(g, tile_h0, tile_w0);
     auto issue = [&](int n) {
         uint64_t* bar = full + (n & 1);
         T* stage = sx0 + (n & 1) * 2 * slot_elems;
-        mbar_expect_tx(bar, mixed ? 2 * slot_bytes : slot_bytes);
-        tma_load_4d(stage, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), first_channel + n * a.chunk, b);
-        if (mixed) tma_load_4d(stage + slot_elems, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), first_channel + n * a.chunk, b);
+        const int c_first = first_channel + n * span;
+        // The second copy brings the same channels again (other border fill) or the next `chunk` channels; a
+        // copy that starts past the last channel is skipped.
+        const bool second = mixed || (n * span + a.chunk < channels);
+        mbar_expect_tx(bar, second ? 2 * slot_bytes : slot_bytes);
+        tma_load_4d(stage, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), c_first, b);
+        if (second) tma_load_4d(stage + slot_elems, &tmap, bar, tile_w0 - g.halo_left(), tile_h0 - g.halo_top(), mixed ? c_first : c_first + a.chunk, b);
     };
     if constexpr (USE_TMA)
     {
@@ -361,15 +367,20 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 }
             }
 
+    // Window of channel c of the stage for a pair of sign s.
+    auto window_of = [&](T* stage, int c, bool negative) {
+        if (mixed) return stage + (negative ? slot_elems : 0) + c * welems;
+        return stage + (c >= a.chunk ? slot_elems + (c - a.chunk) * welems : c * welems);
+    };
     int n = 0;
-    for (int c0 = 0; c0 < channels; c0 += a.chunk, n++)
+    for (int c0 = 0; c0 < channels; c0 += span, n++)
     {
-        const int cc = min(a.chunk, channels - c0);
+        const int cc = min(span, channels - c0);
         T* stage = sx0 + (USE_TMA ? (n & 1) * 2 * slot_elems : 0);
         __syncthreads();
         if constexpr (USE_TMA)
         {
-            if (threadIdx.x == 0 && c0 + a.chunk < channels)
+            if (threadIdx.x == 0 && c0 + span < channels)
             {
                 fence_async_smem();
                 issue(n + 1);
@@ -380,8 +391,8 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
             for (int c = 0; c < cc; c++)
             {
                 const T* src = xb + static_cast<int64_t>(first_channel + c0 + c) * plane;
-                load_window_signed(any_pos ? stage + c * welems : nullptr, any_neg ? stage + (mixed ? slot_elems : 0) + c * welems : nullptr, src, g,
-                                   tile_h0, tile_w0);
+                load_window_signed(any_pos ? window_of(stage, c, false) : nullptr, any_neg ? window_of(stage, c, true) : nullptr, src, g, tile_h0,
+                                   tile_w0);
             }
         }
         for (int e = threadIdx.x; e < cc * OB; e += THREADS)
@@ -414,8 +425,9 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
             if (border)
             {
                 const T* src = xb + static_cast<int64_t>(first_channel + c0) * plane;
-                fix_window_border(stage, src, plane, cc, g, tile_h0, tile_w0, fill0);
+                fix_window_border(stage, src, plane, min(cc, a.chunk), g, tile_h0, tile_w0, fill0);
                 if (mixed) fix_window_border(stage + slot_elems, src, plane, cc, g, tile_h0, tile_w0, Limits<T>::big());
+                else if (cc > a.chunk) fix_window_border(stage + slot_elems, src + a.chunk * plane, plane, cc - a.chunk, g, tile_h0, tile_w0, fill0);
             }
         }
         __syncthreads();
@@ -426,7 +438,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
             for (int o = 0; o < OB; o++)
             {
                 const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
-                const T* win = stage + ((mixed && s < T(0)) ? slot_elems : 0) + c * welems;
+                const T* win = window_of(stage, c, s < T(0));
                 T out[PATCH_H][PATCH_W];
                 if constexpr (KW == 3)
                 {
@@ -508,7 +520,7 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
     // Per channel: two window slots (one per sign) per stage, the structuring elements, signs and scales.
     const size_t window = static_cast<size_t>(a.g.window_elems()) * sizeof(T);
-    const size_t small = (static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);
+    const size_t small = 2 * (static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);  // up to two chunks of channels per stage
     auto plan = [&](int stages, int& chunk, size_t& smem) {
         const size_t per_channel = stages * 2 * window + small, fixed = 128 + stages * 2 * 128;
         if (per_channel + fixed > MAX_SHARED_BYTES) return false;
