@@ -197,11 +197,14 @@ __device__ __forceinline__ void smorph3_softmax(T (&d)[9][PATCH_W], T scale, T (
 /// stride keeps both the writes and the strip reads free of bank conflicts).
 constexpr int RED_ROWS = 10, RED_STRIDE = 33;
 
-/// Backward of one 3 x 3 pair for the thread's patch, see smorph_pair_backward. With d_k = u_k - ref and
-/// out_d = out_u - ref: p_k g = e_k (g / S), pc_k = p_k g (d_k - out_d), c_k = p_k g + |alpha| pc_k and the
-/// alpha gradient is sum_k pc_k d_k. The 9 tap sums and the alpha sum of the 32 lanes are added through the
-/// warp's scratch `red`: every lane stores its 10 values, three lanes per row add a strip of 11 columns
-/// each, two shuffles join the strips.
+/// Backward of one 3 x 3 pair for the thread's patch, see smorph_pair_backward. With d_k = u_k - ref,
+/// out_d = out_u - ref = W / S, W = sum_k e_k d_k, M = sum_k e_k d_k^2 and G = g / S:
+///     c_k = G e_k (1 + |alpha| (d_k - out_d)) = (G (1 - |alpha| out_d)) e_k + (G |alpha|) (e_k d_k),
+///     d out / d alpha = sum_k p_k d_k (d_k - out_d) = (M - out_d W) / S,
+/// so the exponential pass also forms e_k d_k and M, and each tap then costs one multiply and one fused
+/// multiply-add for c_k; the alpha gradient is per pixel, not per tap. The 9 tap sums and the alpha sum of
+/// the 32 lanes are added through the warp's scratch `red`: every lane stores its 10 values, three lanes
+/// per row add a strip of 11 columns each, two shuffles join the strips.
 template <typename T>
 __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win, const T* __restrict__ swk, T* __restrict__ wbin, T* __restrict__ abin,
                                                       T* __restrict__ red, T s, T abs_alpha, T scale, const T (&grad)[PATCH_H][PATCH_W],
@@ -214,22 +217,37 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
     {
-        T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
-        smorph3_values(win, swk, 1, s, g, tx, ty, rr, d);
-        smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+        T ed[9][PATCH_W], e[9][PATCH_W];
+        smorph3_values(win, swk, 1, s, g, tx, ty, rr, ed);   // u_k for now
 #pragma unroll
         for (int j = 0; j < PATCH_W; j++)
         {
-            const T scaled = grad[rr][j] * inv_sum[j];
+            T m = ext3<false>(ed[0][j], ed[1][j], ed[2][j]);
+            m = ext3<false>(m, ed[3][j], ed[4][j]);
+            m = ext3<false>(m, ed[5][j], ed[6][j]);
+            const T ref = ext3<false>(m, ed[7][j], ed[8][j]);
+            T sum = T(0), weighted = T(0), second = T(0);
 #pragma unroll
             for (int k = 0; k < 9; k++)
             {
-                const T pg = e[k][j] * scaled;
-                const T pc = pg * (d[k][j] - out_d[j]);
-                const T c = fma(abs_alpha, pc, pg);
+                const T d = ed[k][j] - ref;
+                e[k][j] = soft_exp(d, scale);
+                sum += e[k][j];
+                ed[k][j] = e[k][j] * d;
+                weighted += ed[k][j];
+                second = fma(ed[k][j], d, second);
+            }
+            const T inv_sum = soft_rcp(sum);
+            const T out_d = weighted * inv_sum;
+            const T scaled = grad[rr][j] * inv_sum;
+            const T ge = scaled * fma(-abs_alpha, out_d, T(1)), ged = scaled * abs_alpha;
+            alpha_sum = fma(scaled, fma(-out_d, weighted, second), alpha_sum);
+#pragma unroll
+            for (int k = 0; k < 9; k++)
+            {
+                const T c = fma(ged, ed[k][j], ge * e[k][j]);
                 gxr[rr + 2 - k / 3][j + 2 - k % 3] += c;
                 tap_sum[k] += c;
-                alpha_sum = fma(pc, d[k][j], alpha_sum);
             }
         }
     }
