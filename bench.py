@@ -408,7 +408,7 @@ def reference_arm(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def run_case(name, batch, device):
@@ -443,7 +443,19 @@ def run_case(name, batch, device):
         if direction == "bwd":
             y.backward(gy)
     torch.cuda.synchronize()
-    print(json.dumps({"case": name, "batch": batch, "done": True}))
+    emit({"case": name, "batch": batch, "done": True})
+
+
+def emit(line):
+    """Write the one JSON line to the process's original stdout."""
+    os.write(RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
+# Libraries (NCCL's version banner, for one) print to stdout from native code. The contract is ONE JSON line
+# on stdout, so everything else is sent to stderr and the result line goes to a duplicate of the original fd.
+sys.stdout.flush()
+RESULT_FD = os.dup(1)
+os.dup2(2, 1)
 
 
 def main():
@@ -502,7 +514,7 @@ def main():
                                     "ms_per_step": ms}
         line["probe_gunits_per_s"] = probe
         line["peaks_gtaps"] = dict(PEAK_GTAPS)
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
