@@ -273,6 +273,166 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Factorised forward (float, square structuring elements up to 7 x 7, merges that need no winner test).
+// exp(|alpha| (u_k - ref)) with u_k = s x_q + s w_k splits into a factor of the pixel and a factor of the tap:
+//     e_k ~ E_q Ew_k,   E_q = 2^(a2 (s x_q - Mx)),   Ew_k = 2^(a2 (s w_k - Mw)),   a2 = |alpha| log2(e),
+// and any common scale cancels in out_u = sum e_k u_k / sum e_k. With A_q = E_q (s x_q - Mx) and
+// Bw_k = Ew_k (s w_k - Mw):
+//     S = sum_k E_q Ew_k,   N = sum_k (A_q Ew_k + E_q Bw_k),   out_u = Mx + Mw + N / S,
+// three fused multiply-adds per tap and no exponential, no maximum. Each warp keeps (E, A) of its own
+// 32 x 8 pixel block plus halo in a private buffer, refreshed when the channel, the sign or |alpha| of
+// the pair changes (pairs that share |alpha| share the buffer), with Mx the largest s x in that block, so
+// E <= 1. The split is exact in real arithmetic; in float it needs 2^(-a2 (range of x in the block + range
+// of w)) to stay a normal number, so a pair whose a2 * range exceeds FACTOR_RANGE (or whose block holds
+// no image pixel, or NaN) takes the stable max-subtracting path instead. All terms of N have one sign, so
+// the quotient loses no digits.
+// ---------------------------------------------------------------------------------------------------
+
+#ifndef MC_PACKED_FMA
+#define MC_PACKED_FMA 1
+#endif
+
+constexpr float FACTOR_RANGE = 80.0f;
+
+template <int KW>
+struct FactorLayout
+{
+    static constexpr int LEN = segment_len(KW, 4), OFF = segment_offset(KW, 4), STRIDE = window_stride(KW, 4);
+    static constexpr int WS = 32 - PATCH_W + LEN;   // columns a warp's 8 threads can read
+    static constexpr int ROWS = 8 + KW - 1;
+    static constexpr int ELEMS = ROWS * WS;
+    static_assert(WS % 4 == 0 && WS <= 64, "the chunk swizzle of the (E, A) buffer covers rows of up to 32 chunks");
+};
+
+/// Smallest and largest in-image x of the warp's block (window elements outside the image hold +-1e30).
+template <int KW>
+__device__ __forceinline__ void factor_range(const float* __restrict__ origin, int lane, float& lo, float& hi)
+{
+    using L = FactorLayout<KW>;
+    constexpr int VECS = L::WS / 4;
+    lo = Limits<float>::inf();
+    hi = -Limits<float>::inf();
+    for (int idx = lane; idx < L::ROWS * VECS; idx += 32)
+    {
+        const int r = idx / VECS, c = idx - r * VECS;
+        const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+        {
+            lo = fminf(lo, e[i] > -1e29f ? e[i] : Limits<float>::inf());
+            hi = fmaxf(hi, e[i] < 1e29f ? e[i] : -Limits<float>::inf());
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+    {
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    }
+}
+
+/// (E, A) of the warp's block for sign s, scale a2 and centre Mx.
+template <int KW>
+__device__ __forceinline__ void factor_fill(const float* __restrict__ origin, float2* __restrict__ ea, float s, float scale, float centre, int lane)
+{
+    using L = FactorLayout<KW>;
+    constexpr int VECS = L::WS / 4;
+    __syncwarp();   // every lane is done with the previous contents
+    for (int idx = lane; idx < L::ROWS * VECS; idx += 32)
+    {
+        const int r = idx / VECS, c = idx - r * VECS;
+        const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
+        const float x0 = fmaf(s, v.x, -centre), x1 = fmaf(s, v.y, -centre), x2 = fmaf(s, v.z, -centre), x3 = fmaf(s, v.w, -centre);
+        const float e0 = soft_exp(x0, scale), e1 = soft_exp(x1, scale), e2 = soft_exp(x2, scale), e3 = soft_exp(x3, scale);
+        float4* dst = reinterpret_cast<float4*>(ea + r * L::WS);   // 16-byte chunks of two (E, A) pairs
+        const int swap = (c >> 2) & 1;
+        dst[(2 * c) ^ swap] = make_float4(e0, e0 * x0, e1, e1 * x1);
+        dst[(2 * c + 1) ^ swap] = make_float4(e2, e2 * x2, e3, e3 * x3);
+    }
+    __syncwarp();
+}
+
+/// S and N of one pair for the thread's patch: acc = (S, sum A Ew), rest = sum E Bw, N = acc.y + rest.
+/// `eb` holds (Ew_k, Bw_k) of the pair, element k at eb[k * wstride]. Every row of the (E, A) block is loaded
+/// once and serves the kernel rows of both patch rows that read it.
+template <int KW>
+__device__ __forceinline__ void factor_pair(const float2* __restrict__ ea, const float2* __restrict__ eb, int wstride, int lane,
+                                            float2 (&acc)[PATCH_H][PATCH_W], float (&rest)[PATCH_H][PATCH_W])
+{
+    using L = FactorLayout<KW>;
+    static_assert(PATCH_H == 2, "the row schedule below is written for two patch rows");
+    const float4* base = reinterpret_cast<const float4*>(ea + ((lane >> 3) * PATCH_H) * L::WS);
+    // Chunk G of a row (two pixels, 16 bytes) is stored at G ^ ((G >> 3) & 1): with the plain order the 8 lanes
+    // of a quarter warp, 32 bytes apart, would hit every bank twice.
+    int chunk[L::LEN / 2];
+#pragma unroll
+    for (int v = 0; v < L::LEN / 2; v++)
+    {
+        const int G = 2 * (lane & 7) + v;
+        chunk[v] = G ^ ((G >> 3) & 1);
+    }
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            acc[rr][j] = make_float2(0.0f, 0.0f);
+            rest[rr][j] = 0.0f;
+        }
+    // Block row r (relative to the thread's first patch row) is read by patch row rr through kernel row kh = rr + KW - 1 - r.
+    auto row = [&](int r, bool first, bool second) {
+        float2 seg[L::LEN];
+        const float4* src = base + r * (L::WS / 2);
+#pragma unroll
+        for (int v = 0; v < L::LEN / 2; v++)
+        {
+            const float4 t = src[chunk[v]];
+            seg[2 * v] = make_float2(t.x, t.y);
+            seg[2 * v + 1] = make_float2(t.z, t.w);
+        }
+        auto apply = [&](int rr, int kh) {
+#pragma unroll
+            for (int kw = 0; kw < KW; kw++)
+            {
+                const float2 t = eb[(kh * KW + kw) * wstride];
+                const float2 ew2 = make_float2(t.x, t.x);
+#pragma unroll
+                for (int j = 0; j < PATCH_W; j++)
+                {
+                    const float2 q = seg[L::OFF + j + KW - 1 - kw];
+#if MC_PACKED_FMA
+                    acc[rr][j] = __ffma2_rn(q, ew2, acc[rr][j]);
+#else
+                    acc[rr][j].x = fmaf(q.x, ew2.x, acc[rr][j].x);
+                    acc[rr][j].y = fmaf(q.y, ew2.y, acc[rr][j].y);
+#endif
+                    rest[rr][j] = fmaf(q.x, t.y, rest[rr][j]);
+                }
+            }
+        };
+        if (first) apply(0, KW - 1 - r);
+        if (second) apply(1, KW - r);
+    };
+    row(0, true, false);
+    if constexpr (KW == 3)
+    {
+#pragma unroll
+        for (int r = 1; r < KW; r++) row(r, true, true);
+    }
+    else
+    {
+#pragma unroll 1
+        for (int r = 1; r < KW; r++) row(r, true, true);
+    }
+    row(KW, false, true);
+}
+
+template <typename T, int KW, bool STATS>
+__host__ __device__ constexpr bool can_factorise() { return sizeof(T) == 4 && !STATS && KW >= 3 && KW <= 7; }
+
 template <typename T>
 struct SmorphForwardArgs
 {
@@ -286,6 +446,7 @@ struct SmorphForwardArgs
     int merge;
     int o_groups;
     int chunk;
+    int factorise;    // use the factorised path where it is safe (merges without winner test)
     unsigned int* errors;  // counter of timed-out waits
 };
 
@@ -308,6 +469,12 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     T* sx0 = reinterpret_cast<T*>(smem_raw + 128);
     T* sw = sx0 + (USE_TMA ? 2 : 1) * 2 * slot_elems;   // [2 chunk][taps][OB], sign folded
     T* sa = sw + 2 * a.chunk * taps * OB;                 // [2 chunk][OB][2]: sign, exp scale
+    // Factorised path: [2 chunk][taps][OB] (Ew, Bw), [2 chunk][OB] (Mw, range of w), then one (E, A) buffer per warp.
+    constexpr bool FACTOR = can_factorise<T, KW, STATS>();
+    float2* seb = reinterpret_cast<float2*>(smem_raw + (reinterpret_cast<unsigned char*>(sa + 2 * a.chunk * OB * 2) - smem_raw + 15) / 16 * 16);
+    float2* spair = seb + 2 * a.chunk * taps * OB;
+    float2* sea = spair + 2 * a.chunk * OB + (threadIdx.x >> 5) * FactorLayout<FACTOR ? KW : 3>::ELEMS;
+    const bool factorise = FACTOR && a.factorise != 0;
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int og = blockIdx.x % a.o_groups;
@@ -385,6 +552,10 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 }
             }
 
+    [[maybe_unused]] T offset[OB];   // factorised path: per-channel constant part of the sum
+#pragma unroll
+    for (int o = 0; o < OB; o++) offset[o] = T(0);
+
     // Window of channel c of the stage for a pair of sign s.
     auto window_of = [&](T* stage, int c, bool negative) {
         if (mixed) return stage + (negative ? slot_elems : 0) + c * welems;
@@ -433,6 +604,46 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
             }
             sw[e] = al >= T(0) ? v : -v;
         }
+        if constexpr (FACTOR)
+        {
+            if (factorise)
+            {
+                // One warp per pair, one lane per tap: Mw and the range of s w by shuffles, then (Ew, Bw).
+                const int lane = threadIdx.x & 31;
+                for (int e = threadIdx.x >> 5; e < cc * OB; e += THREADS / 32)
+                {
+                    const int o = e % OB, c = e / OB;
+                    if (o0 + o >= g.Co)
+                    {
+                        if (lane == 0) spair[e] = make_float2(0.0f, Limits<float>::inf());   // never factorised
+                        continue;
+                    }
+                    const float al = __ldg(a.alpha + (g.identity ? o0 + o : static_cast<int64_t>(o0 + o) * g.Ci + c0 + c));
+                    const float sgn = al >= 0.0f ? 1.0f : -1.0f, scale = exp_scale(fabsf(al));
+                    const float* wp = a.w + (static_cast<int64_t>(o0 + o) * wci + (g.identity ? 0 : c0 + c)) * taps;
+                    float lo = Limits<float>::inf(), hi = -Limits<float>::inf();
+                    for (int k = lane; k < taps; k += 32)
+                    {
+                        const float v = sgn * __ldg(wp + k);
+                        lo = fminf(lo, v);
+                        hi = fmaxf(hi, v);
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1)
+                    {
+                        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+                        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+                    }
+                    if (lane == 0) spair[e] = make_float2(hi, hi - lo);
+                    for (int k = lane; k < taps; k += 32)
+                    {
+                        const float d = sgn * __ldg(wp + k) - hi;
+                        const float ew = soft_exp(d, scale);
+                        seb[(c * taps + k) * OB + o] = make_float2(ew, ew * d);
+                    }
+                }
+            }
+        }
         if constexpr (USE_TMA)
         {
             if (!mbar_wait(full + (n & 1), (n >> 1) & 1))
@@ -452,12 +663,51 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
 
         for (int c = 0; c < cc && warp_live; c++)
         {
+            // Factorised path: range of x in the warp's block (once per channel) and what the warp's buffer holds.
+            [[maybe_unused]] float x_lo = 0.0f, x_hi = 0.0f, held_s = 0.0f, held_scale = -1.0f, held_centre = 0.0f;
+            [[maybe_unused]] bool have_range = false;
 #pragma unroll
             for (int o = 0; o < OB; o++)
             {
                 const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
                 const T* win = window_of(stage, c, s < T(0));
                 T out[PATCH_H][PATCH_W];
+                if constexpr (FACTOR)
+                {
+                    if (factorise)
+                    {
+                        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+                        const float* origin = win + (8 * (warp >> 1)) * FactorLayout<KW>::STRIDE + 32 * (warp & 1);
+                        if (!have_range)
+                        {
+                            factor_range<KW>(origin, lane, x_lo, x_hi);
+                            have_range = true;
+                        }
+                        const float2 pr = spair[c * OB + o];   // (Mw, range of w)
+                        if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE)
+                        {
+                            if (!(held_s == s && held_scale == scale))
+                            {
+                                held_centre = s > 0.0f ? x_hi : -x_lo;
+                                factor_fill<KW>(origin, sea, s, scale, held_centre, lane);
+                                held_s = s;
+                                held_scale = scale;
+                            }
+                            float2 acc[PATCH_H][PATCH_W];
+                            float rest[PATCH_H][PATCH_W];
+                            factor_pair<KW>(sea, seb + c * taps * OB + o, OB, lane, acc, rest);
+                            // out = s (Mx + Mw + N / S); the merge is a sum (a lone pair for identity), so the
+                            // constant part is added up per output channel and joins the pixels at the end.
+                            offset[o] += s * (held_centre + pr.x);
+#pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                                for (int j = 0; j < PATCH_W; j++)
+                                    merged[o][rr][j] = fmaf((acc[rr][j].y + rest[rr][j]) * soft_rcp(acc[rr][j].x), s, merged[o][rr][j]);
+                            continue;
+                        }
+                    }
+                }
                 if constexpr (KW == 3)
                 {
 #pragma unroll
@@ -506,7 +756,9 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
             {
                 const int h = tile_h0 + ty * PATCH_H + rr, w = tile_w0 + tx * PATCH_W + j;
                 if (o0 + o >= g.Co || h >= g.H || w >= g.W) continue;
-                const T v = (!STATS && a.merge == MC_MERGE_AVERAGE) ? merged[o][rr][j] / divisor : merged[o][rr][j];
+                T v = merged[o][rr][j];
+                if constexpr (FACTOR) v += offset[o];
+                if (!STATS && a.merge == MC_MERGE_AVERAGE) v = v / divisor;
                 dst[((static_cast<int64_t>(b) * g.Co + o0 + o) * g.H + h) * g.W + w] = v;
             }
 }
@@ -538,16 +790,26 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
     // Per channel: two window slots (one per sign) per stage, the structuring elements, signs and scales.
     const size_t window = static_cast<size_t>(a.g.window_elems()) * sizeof(T);
-    const size_t small = 2 * (static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);  // up to two chunks of channels per stage
+    const bool stats = counts != nullptr;
+    // The factorised path suits merges without a winner test: MAX / MIN compare the recomputed soft extremum
+    // with the stored output within 1e-6, which only the same arithmetic in every pass guarantees.
+    constexpr bool FACTOR = can_factorise<T, KW, false>();
+    a.factorise = FACTOR && !stats && d.merge != MC_MERGE_MAX && d.merge != MC_MERGE_MIN;
+    size_t small = 2 * (static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);  // up to two chunks of channels per stage
+    size_t extra = 0;
+    if (a.factorise)
+    {
+        small += 2 * (static_cast<size_t>(a.g.taps()) * OB + OB) * sizeof(float2);
+        extra = 16 + (THREADS / 32) * static_cast<size_t>(FactorLayout<FACTOR ? KW : 3>::ELEMS) * sizeof(float2);
+    }
     auto plan = [&](int stages, int& chunk, size_t& smem) {
-        const size_t per_channel = stages * 2 * window + small, fixed = 128 + stages * 2 * 128;
+        const size_t per_channel = stages * 2 * window + small, fixed = 128 + stages * 2 * 128 + extra;
         if (per_channel + fixed > MAX_SHARED_BYTES) return false;
-        chunk = static_cast<int>((100 * 1024 - fixed) / per_channel);
+        chunk = static_cast<int>(((a.factorise ? 112 : 100) * 1024 - fixed) / per_channel);
         chunk = std::max(1, std::min(std::min(chunk, 8), channels));
         smem = fixed + per_channel * chunk;
         return true;
     };
-    const bool stats = counts != nullptr;
     CUtensorMap tmap{};
     int chunk = 1;
     size_t smem = 0;

@@ -16,6 +16,12 @@ int smorph_forward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const M
     const bool wide = d.merge != MC_MERGE_IDENTITY && d.Co >= 2;
     return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
+        // The factorised path has registers to spare: four output channels share every (E, A) buffer.
+        if constexpr (can_factorise<T, KW, false>())
+        {
+            if (counts == nullptr && d.Co >= 4 && (d.merge == MC_MERGE_ADD || d.merge == MC_MERGE_AVERAGE))
+                return launch_smorph_forward<T, KW, 4>(d, x, w, alpha, y, target, counts, stream);
+        }
         return wide ? launch_smorph_forward<T, KW, 2>(d, x, w, alpha, y, target, counts, stream)
                     : launch_smorph_forward<T, KW, 1>(d, x, w, alpha, y, target, counts, stream);
     });

@@ -95,28 +95,47 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 
 /// After a TMA copy of a window (zero filled outside the image): overwrite the out-of-image elements of
 /// `channels` staged windows with the border rule. Only CTAs whose window leaves the image call this.
+/// Only the part of the window that a live warp can read is visited (see thread_patch: the warps of a
+/// partial tile whose 32 x 8 block lies outside the image do no arithmetic), which for the half-empty last
+/// tile column of a 224-wide image is 4 columns instead of 36.
 template <typename T>
 __device__ __forceinline__ void fix_window_border(T* __restrict__ win, const T* __restrict__ planes, int64_t plane_stride, int channels,
                                                   const Geometry& g, int tile_h0, int tile_w0, T outside)
 {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
-    // Columns [0, n_left) and [first_right, stride) of a row inside the image lie outside it.
-    const int n_left = min(max(-col0, 0), g.win_stride);
-    const int first_right = min(max(g.W - col0, 0), g.win_stride);
-    const int n_side = n_left + g.win_stride - first_right;
-    for (int r = warp; r < g.win_rows * channels; r += THREADS / 32)
+    const int live_cols = g.win_stride - 32 * (TILE_W / 32 - (min(g.W - tile_w0, TILE_W) + 31) / 32);
+    const int live_rows = g.win_rows - 8 * (TILE_H / 8 - (min(g.H - tile_h0, TILE_H) + 7) / 8);
+    // Window rows [r_lo, r_hi) are image rows; of those, columns [0, n_left) and [first_right, live_cols) lie outside.
+    const int r_lo = min(max(-row0, 0), live_rows), r_hi = min(max(g.H - row0, 0), live_rows);
+    const int n_left = min(max(-col0, 0), live_cols);
+    const int first_right = min(max(g.W - col0, 0), live_cols);
+    const int n_side = n_left + live_cols - first_right;
+    const int welems = g.window_elems();
+    auto put = [&](int c, int wr, int col) {
+        T v = outside;
+        if (g.replicate)
+            v = __ldg(planes + c * plane_stride + static_cast<int64_t>(min(max(row0 + wr, 0), g.H - 1)) * g.W + min(max(col0 + col, 0), g.W - 1));
+        win[c * welems + wr * g.win_stride + col] = v;
+    };
+    if (n_side > 0)
     {
-        const int c = r / g.win_rows, wr = r % g.win_rows;
-        const int iy = row0 + wr;
-        const bool row_in = iy >= 0 && iy < g.H;
-        const T* src = planes + c * plane_stride + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W;
-        T* out = win + static_cast<int64_t>(c) * g.window_elems() + wr * g.win_stride;
-        const int count = row_in ? n_side : g.win_stride;
-        for (int e = lane; e < count; e += 32)
+        const int per_channel = (r_hi - r_lo) * n_side;
+        for (int e = threadIdx.x; e < channels * per_channel; e += THREADS)
         {
-            const int col = (!row_in || e < n_left) ? e : first_right + e - n_left;
-            out[col] = g.replicate ? __ldg(src + min(max(col0 + col, 0), g.W - 1)) : outside;
+            const int c = e / per_channel, rest = e - c * per_channel;
+            const int r = rest / n_side, i = rest - r * n_side;
+            put(c, r_lo + r, i < n_left ? i : first_right + i - n_left);
+        }
+    }
+    const int n_out = r_lo + live_rows - r_hi;   // rows above and below the image
+    if (n_out > 0)
+    {
+        const int per_channel = n_out * live_cols;
+        for (int e = threadIdx.x; e < channels * per_channel; e += THREADS)
+        {
+            const int c = e / per_channel, rest = e - c * per_channel;
+            const int r = rest / live_cols, col = rest - r * live_cols;
+            put(c, r < r_lo ? r : r_hi + r - r_lo, col);
         }
     }
 }

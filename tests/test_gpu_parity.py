@@ -338,5 +338,6 @@ def test_results_are_reproducible_run_to_run(C):
     assert torch.equal(a, b) and torch.equal(ia, ib)
     g1 = C.morpho_backward("erosion", x, wk, gy, "sum", "replicate")
     g2 = C.morpho_backward("erosion", x, wk, gy, "sum", "replicate")
-    torch.testing.assert_close(g1[0], g2[0], rtol=1e-5, atol=1e-5)
+    # up to 32 x 25 float atomics per element, in an order that changes from run to run
+    torch.testing.assert_close(g1[0], g2[0], rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(g1[1], g2[1], rtol=1e-4, atol=1e-2)
