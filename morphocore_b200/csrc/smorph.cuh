@@ -300,32 +300,43 @@ template <int KW>
 struct FactorLayout
 {
     static constexpr int LEN = segment_len(KW, 4), OFF = segment_offset(KW, 4), STRIDE = window_stride(KW, 4);
-    static constexpr int WS = 32 - PATCH_W + LEN;   // columns a warp's 8 threads can read
+    static constexpr int WS = 32 - PATCH_W + LEN;   // columns of the x window a warp's 8 x 4 threads can read
     static constexpr int ROWS = 8 + KW - 1;
-    static constexpr int ELEMS = ROWS * WS;
-    static_assert(WS % 4 == 0 && WS <= 64, "the chunk swizzle of the (E, A) buffer covers rows of up to 32 chunks");
+    static constexpr int VECS = WS / 4;             // 128-bit vectors of x per row
+    // The (E, A) block is stored in 16-byte chunks of two pixels. Thread column t (0..7) reads the LEN / 2
+    // chunks from 2 t on. In one plain row the 8 lanes of a quarter warp, 32 bytes apart, would hit every bank
+    // twice, so a row holds two copies: chunks [0, HALF) for t < 4 and, an odd number of chunks further,
+    // chunks [8, 8 + HALF) for t >= 4. The two groups of lanes then cover all 32 banks, and every load is the
+    // lane's base plus a compile-time offset.
+    static constexpr int HALF = 6 + LEN / 2;
+    static constexpr int SECOND = HALF % 2 == 0 ? HALF + 1 : HALF;   // chunk at which the second copy starts
+    static constexpr int ROW_CHUNKS = SECOND + HALF;
+    static constexpr int BYTES = ROWS * ROW_CHUNKS * 16;
+    static_assert(WS % 4 == 0 && HALF % 2 == 0 && 2 * (8 + HALF) >= WS, "the two copies cover the row");
 };
 
 /// Smallest and largest in-image x of the warp's block (window elements outside the image hold +-1e30).
+/// Lanes 0 .. 3 VECS - 1 each own one vector column of every third row.
 template <int KW>
 __device__ __forceinline__ void factor_range(const float* __restrict__ origin, int lane, float& lo, float& hi)
 {
     using L = FactorLayout<KW>;
-    constexpr int VECS = L::WS / 4;
+    static_assert(3 * L::VECS <= 32, "three rows per sweep");
     lo = Limits<float>::inf();
     hi = -Limits<float>::inf();
-    for (int idx = lane; idx < L::ROWS * VECS; idx += 32)
-    {
-        const int r = idx / VECS, c = idx - r * VECS;
-        const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
-        const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++)
+    const int r0 = lane / L::VECS, c = lane - r0 * L::VECS;
+    if (r0 < 3)
+        for (int r = r0; r < L::ROWS; r += 3)
         {
-            lo = fminf(lo, e[i] > -1e29f ? e[i] : Limits<float>::inf());
-            hi = fmaxf(hi, e[i] < 1e29f ? e[i] : -Limits<float>::inf());
+            const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+            {
+                lo = fminf(lo, e[i] > -1e29f ? e[i] : Limits<float>::inf());
+                hi = fmaxf(hi, e[i] < 1e29f ? e[i] : -Limits<float>::inf());
+            }
         }
-    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1)
     {
@@ -336,22 +347,30 @@ __device__ __forceinline__ void factor_range(const float* __restrict__ origin, i
 
 /// (E, A) of the warp's block for sign s, scale a2 and centre Mx.
 template <int KW>
-__device__ __forceinline__ void factor_fill(const float* __restrict__ origin, float2* __restrict__ ea, float s, float scale, float centre, int lane)
+__device__ __forceinline__ void factor_fill(const float* __restrict__ origin, float4* __restrict__ ea, float s, float scale, float centre, int lane)
 {
     using L = FactorLayout<KW>;
-    constexpr int VECS = L::WS / 4;
     __syncwarp();   // every lane is done with the previous contents
-    for (int idx = lane; idx < L::ROWS * VECS; idx += 32)
-    {
-        const int r = idx / VECS, c = idx - r * VECS;
-        const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
-        const float x0 = fmaf(s, v.x, -centre), x1 = fmaf(s, v.y, -centre), x2 = fmaf(s, v.z, -centre), x3 = fmaf(s, v.w, -centre);
-        const float e0 = soft_exp(x0, scale), e1 = soft_exp(x1, scale), e2 = soft_exp(x2, scale), e3 = soft_exp(x3, scale);
-        float4* dst = reinterpret_cast<float4*>(ea + r * L::WS);   // 16-byte chunks of two (E, A) pairs
-        const int swap = (c >> 2) & 1;
-        dst[(2 * c) ^ swap] = make_float4(e0, e0 * x0, e1, e1 * x1);
-        dst[(2 * c + 1) ^ swap] = make_float4(e2, e2 * x2, e3, e3 * x3);
-    }
+    const int r0 = lane / L::VECS, c = lane - r0 * L::VECS;
+    if (r0 < 3)
+        for (int r = r0; r < L::ROWS; r += 3)
+        {
+            const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
+            const float x0 = fmaf(s, v.x, -centre), x1 = fmaf(s, v.y, -centre), x2 = fmaf(s, v.z, -centre), x3 = fmaf(s, v.w, -centre);
+            const float e0 = soft_exp(x0, scale), e1 = soft_exp(x1, scale), e2 = soft_exp(x2, scale), e3 = soft_exp(x3, scale);
+            const float4 first = make_float4(e0, e0 * x0, e1, e1 * x1), second = make_float4(e2, e2 * x2, e3, e3 * x3);
+            float4* row = ea + r * L::ROW_CHUNKS;
+            if (2 * c < L::HALF)   // HALF is even: both chunks of the vector fall on the same side
+            {
+                row[2 * c] = first;
+                row[2 * c + 1] = second;
+            }
+            if (2 * c >= 8)
+            {
+                row[L::SECOND + 2 * c - 8] = first;
+                row[L::SECOND + 2 * c - 7] = second;
+            }
+        }
     __syncwarp();
 }
 
@@ -359,21 +378,13 @@ __device__ __forceinline__ void factor_fill(const float* __restrict__ origin, fl
 /// `eb` holds (Ew_k, Bw_k) of the pair, element k at eb[k * wstride]. Every row of the (E, A) block is loaded
 /// once and serves the kernel rows of both patch rows that read it.
 template <int KW>
-__device__ __forceinline__ void factor_pair(const float2* __restrict__ ea, const float2* __restrict__ eb, int wstride, int lane,
+__device__ __forceinline__ void factor_pair(const float4* __restrict__ ea, const float2* __restrict__ eb, int wstride, int lane,
                                             float2 (&acc)[PATCH_H][PATCH_W], float (&rest)[PATCH_H][PATCH_W])
 {
     using L = FactorLayout<KW>;
     static_assert(PATCH_H == 2, "the row schedule below is written for two patch rows");
-    const float4* base = reinterpret_cast<const float4*>(ea + ((lane >> 3) * PATCH_H) * L::WS);
-    // Chunk G of a row (two pixels, 16 bytes) is stored at G ^ ((G >> 3) & 1): with the plain order the 8 lanes
-    // of a quarter warp, 32 bytes apart, would hit every bank twice.
-    int chunk[L::LEN / 2];
-#pragma unroll
-    for (int v = 0; v < L::LEN / 2; v++)
-    {
-        const int G = 2 * (lane & 7) + v;
-        chunk[v] = G ^ ((G >> 3) & 1);
-    }
+    const int t = lane & 7;
+    const float4* base = ea + ((lane >> 3) * PATCH_H) * L::ROW_CHUNKS + (t < 4 ? 2 * t : L::SECOND + 2 * t - 8);
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -385,11 +396,11 @@ __device__ __forceinline__ void factor_pair(const float2* __restrict__ ea, const
     // Block row r (relative to the thread's first patch row) is read by patch row rr through kernel row kh = rr + KW - 1 - r.
     auto row = [&](int r, bool first, bool second) {
         float2 seg[L::LEN];
-        const float4* src = base + r * (L::WS / 2);
+        const float4* src = base + r * L::ROW_CHUNKS;
 #pragma unroll
         for (int v = 0; v < L::LEN / 2; v++)
         {
-            const float4 t = src[chunk[v]];
+            const float4 t = src[v];
             seg[2 * v] = make_float2(t.x, t.y);
             seg[2 * v + 1] = make_float2(t.z, t.w);
         }
@@ -433,6 +444,105 @@ __device__ __forceinline__ void factor_pair(const float2* __restrict__ ea, const
 template <typename T, int KW, bool STATS>
 __host__ __device__ constexpr bool can_factorise() { return sizeof(T) == 4 && !STATS && KW >= 3 && KW <= 7; }
 
+/// 2^x, hardware approximation (flushes denormal results to zero).
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+    return e;
+}
+
+/// float version of smorph3_pair_backward on pairs of horizontally adjacent pixels: apart from the values
+/// u_k, the maximum, the exponentials and the register window of grad_input, every step is a packed
+/// two-lane instruction (add.f32x2, mul.f32x2, fma.rn.f32x2), half the issue slots of the scalar form.
+__device__ __forceinline__ void smorph3_pair_backward(const float* __restrict__ win, const float* __restrict__ swk, float* __restrict__ wbin,
+                                                      float* __restrict__ abin, float* __restrict__ red, float s, float abs_alpha, float scale,
+                                                      const float (&grad)[PATCH_H][PATCH_W], const Geometry& g, int tx, int ty, int lane,
+                                                      float (&gxr)[PATCH_H + 2][PATCH_W + 2])
+{
+    constexpr int OFF = segment_offset(3, 4), STRIDE = window_stride(3, 4);
+    float2 tap_sum[9];
+#pragma unroll
+    for (int k = 0; k < 9; k++) tap_sum[k] = make_float2(0.0f, 0.0f);
+    float2 alpha_sum = make_float2(0.0f, 0.0f);
+    const float2 scale2 = make_float2(scale, scale), alpha2 = make_float2(abs_alpha, abs_alpha), minus_alpha2 = make_float2(-abs_alpha, -abs_alpha);
+    const float2 one2 = make_float2(1.0f, 1.0f);
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int jp = 0; jp < PATCH_W / 2; jp++)
+        {
+            // The two pixels read segment columns first .. first + 3: two aligned 128-bit loads per window row.
+            const int first = OFF + 2 * jp, quad = first / 4, base = first - 4 * quad;
+            float2 d[9], e[9];
+#pragma unroll
+            for (int kh = 0; kh < 3; kh++)
+            {
+                float seg[8];
+                const float* row = win + (ty * PATCH_H + rr + 2 - kh) * STRIDE + tx * PATCH_W + 4 * quad;
+                lds128(seg, row);
+                lds128(seg + 4, row + 4);
+#pragma unroll
+                for (int kw = 0; kw < 3; kw++)
+                {
+                    const float wv = swk[kh * 3 + kw];
+                    d[kh * 3 + kw] = make_float2(fmaf(s, seg[base + 2 - kw], wv), fmaf(s, seg[base + 3 - kw], wv));   // u_k for now
+                }
+            }
+            float mx = ext3<false>(d[0].x, d[1].x, d[2].x), my = ext3<false>(d[0].y, d[1].y, d[2].y);
+            mx = ext3<false>(mx, d[3].x, d[4].x); my = ext3<false>(my, d[3].y, d[4].y);
+            mx = ext3<false>(mx, d[5].x, d[6].x); my = ext3<false>(my, d[5].y, d[6].y);
+            mx = ext3<false>(mx, d[7].x, d[8].x); my = ext3<false>(my, d[7].y, d[8].y);
+            const float2 minus_ref = make_float2(-mx, -my);
+            float2 sum = make_float2(0.0f, 0.0f), weighted = sum, second = sum;
+#pragma unroll
+            for (int k = 0; k < 9; k++)
+            {
+                const float2 dk = __fadd2_rn(d[k], minus_ref);
+                const float2 t = __fmul2_rn(dk, scale2);
+                e[k] = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+                sum = __fadd2_rn(sum, e[k]);
+                d[k] = __fmul2_rn(e[k], dk);   // e_k d_k from here on: exactly zero for excluded taps, whose d_k is -1e30
+                weighted = __fadd2_rn(weighted, d[k]);
+                second = __ffma2_rn(d[k], dk, second);
+            }
+            const float2 inv_sum = make_float2(soft_rcp(sum.x), soft_rcp(sum.y));
+            const float2 out_d = __fmul2_rn(weighted, inv_sum);
+            const float2 scaled = __fmul2_rn(make_float2(grad[rr][2 * jp], grad[rr][2 * jp + 1]), inv_sum);
+            const float2 ge = __fmul2_rn(scaled, __ffma2_rn(minus_alpha2, out_d, one2)), ged = __fmul2_rn(scaled, alpha2);
+            const float2 minus_out_d = make_float2(-out_d.x, -out_d.y);
+            alpha_sum = __ffma2_rn(scaled, __ffma2_rn(minus_out_d, weighted, second), alpha_sum);
+#pragma unroll
+            for (int k = 0; k < 9; k++)
+            {
+                const float2 c = __ffma2_rn(ged, d[k], __fmul2_rn(ge, e[k]));
+                gxr[rr + 2 - k / 3][2 * jp + 2 - k % 3] += c.x;
+                gxr[rr + 2 - k / 3][2 * jp + 3 - k % 3] += c.y;
+                tap_sum[k] = __fadd2_rn(tap_sum[k], c);
+            }
+        }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 9; k++) red[k * RED_STRIDE + lane] = tap_sum[k].x + tap_sum[k].y;
+    red[9 * RED_STRIDE + lane] = alpha_sum.x + alpha_sum.y;
+    __syncwarp();
+    float part = 0.0f;
+    if (lane < 3 * RED_ROWS)
+    {
+        const float* strip = red + (lane / 3) * RED_STRIDE + (lane % 3) * 11;
+        const int n = (lane % 3) == 2 ? 10 : 11;
+#pragma unroll
+        for (int c = 0; c < 11; c++)
+            if (c < n) part += strip[c];
+    }
+    part += __shfl_down_sync(0xffffffffu, part, 1) + __shfl_down_sync(0xffffffffu, part, 2);
+    if (lane < 3 * RED_ROWS && lane % 3 == 0)
+    {
+        if (lane < 27) wbin[lane / 3] = part;
+        else *abin = part;
+    }
+}
+
 template <typename T>
 struct SmorphForwardArgs
 {
@@ -473,7 +583,8 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     constexpr bool FACTOR = can_factorise<T, KW, STATS>();
     float2* seb = reinterpret_cast<float2*>(smem_raw + (reinterpret_cast<unsigned char*>(sa + 2 * a.chunk * OB * 2) - smem_raw + 15) / 16 * 16);
     float2* spair = seb + 2 * a.chunk * taps * OB;
-    float2* sea = spair + 2 * a.chunk * OB + (threadIdx.x >> 5) * FactorLayout<FACTOR ? KW : 3>::ELEMS;
+    float4* sea = reinterpret_cast<float4*>(smem_raw + (reinterpret_cast<unsigned char*>(spair + 2 * a.chunk * OB) - smem_raw + 15) / 16 * 16)
+                  + (threadIdx.x >> 5) * (FactorLayout<FACTOR ? KW : 3>::BYTES / 16);
     const bool factorise = FACTOR && a.factorise != 0;
 
     const int tiles = g.tiles_x * g.tiles_y;
@@ -800,7 +911,7 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     if (a.factorise)
     {
         small += 2 * (static_cast<size_t>(a.g.taps()) * OB + OB) * sizeof(float2);
-        extra = 16 + (THREADS / 32) * static_cast<size_t>(FactorLayout<FACTOR ? KW : 3>::ELEMS) * sizeof(float2);
+        extra = 32 + (THREADS / 32) * static_cast<size_t>(FactorLayout<FACTOR ? KW : 3>::BYTES);
     }
     auto plan = [&](int stages, int& chunk, size_t& smem) {
         const size_t per_channel = stages * 2 * window + small, fixed = 128 + stages * 2 * 128 + extra;
