@@ -41,9 +41,9 @@ UNIT = "Gtaps/s"
 # the run by morphocore_b200/probe_rates (register-only kernels, every operand loop carried). The values
 # below are an earlier measurement on this pool's B200 (profiles/probe_rates_b200.md), used only when the
 # probe binary is missing. A dilation / erosion tap is one add and one max; the float peak is the best mix
-# found (packed add.f32x2 + 3-input max), the double peak DADD + compare/select; a smorph tap costs one ex2
-# forward and two backward (forward state recomputed, then the per-tap weights).
-PEAK_GTAPS = {"morph_f32": 27300.0, "morph_f64": 5750.0, "smorph_fwd_f32": 4633.0, "smorph_bwd_f32": 2316.0}
+# found (packed add.f32x2 + 3-input max), the double peak DADD + compare/select; a smorph tap costs three
+# fused multiply-adds forward (factorised exponentials) and eleven FP32 operations plus one ex2 backward.
+PEAK_GTAPS = {"morph_f32": 27300.0, "morph_f64": 5750.0, "smorph_fwd_f32": 10078.0, "smorph_bwd_f32": 2748.0, "smorph_fwdbwd_f32": 2159.0}
 PEAK_SOURCE = "earlier measurement on this pool (probe binary missing)"
 
 
@@ -58,8 +58,11 @@ def measure_peaks():
         r = json.loads(out)
         PEAK_GTAPS["morph_f32"] = max(r["add_max_taps"], r["add_max3_taps"], r["add2_max3_taps"])
         PEAK_GTAPS["morph_f64"] = max(r["f64_add_fmax_taps"], r["f64_add_select_taps"])
-        PEAK_GTAPS["smorph_fwd_f32"] = r["ex2_ops"]
-        PEAK_GTAPS["smorph_bwd_f32"] = r["ex2_ops"] / 2
+        # smorph forward (sum / mean / identity merges): the factorised kernel needs 3 fused multiply-adds per tap and
+        # no exponential; smorph backward: 11 FP32 operations and one ex2 per tap (kernel table).
+        PEAK_GTAPS["smorph_fwd_f32"] = r["fma_ops"] / 3
+        PEAK_GTAPS["smorph_bwd_f32"] = min(r["ex2_ops"], r["fma_ops"] / 11)
+        PEAK_GTAPS["smorph_fwdbwd_f32"] = 1.0 / (1.0 / PEAK_GTAPS["smorph_fwd_f32"] + 1.0 / PEAK_GTAPS["smorph_bwd_f32"])
         PEAK_SOURCE = "of measured (instruction-rate probe run on this GPU at the start of this bench)"
         return r
     except (OSError, ValueError, KeyError, IndexError, subprocess.TimeoutExpired):
@@ -345,9 +348,9 @@ def run_single(name, device, steps, warmup):
         for alpha in WL.CFG3_ALPHAS:
             c = WL.cfg3(alpha)
             x, w, a, gy = c["x"].to(device).requires_grad_(True), c["w"].to(device).requires_grad_(True), c["alpha"].to(device).requires_grad_(True), c["gy"].to(device)
-            # one ex2 per tap forward, two backward: 3 per forward+backward pair
             results[f"cfg3 smorph fwd+bwd fp32 mean alpha={alpha:g} (16,32,128,128)x(32,32,7,7)"] = timed(
-                lambda: F.smorph(x, w, a, channel_merge_mode="mean"), gy, c["n_taps"], "smorph_fwd_f32", {"peak_note": "peak is the forward (1 ex2/tap) ceiling; fwd+bwd at 3 ex2/tap is a third of it"})
+                lambda: F.smorph(x, w, a, channel_merge_mode="mean"), gy, c["n_taps"], "smorph_fwdbwd_f32",
+                {"peak_note": "peak of a forward+backward pair: 3 FMA per tap forward, 11 FP32 operations + 1 ex2 per tap backward"})
             del x, w, a, gy
     if name in ("cfg4", "all"):
         for op in ("dilation", "erosion"):

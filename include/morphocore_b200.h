@@ -28,7 +28,8 @@ extern "C" {
 enum mc_op { MC_OP_DILATION = 0, MC_OP_EROSION = 1 };
 
 /* Channel merge, the integers of MORPHO_MERGE (CPP/morpho_op_enum.hpp:18-26) that
- * morphocore/functional/merge_enum.py:4-11 sends through the operator schema. SMOOTH (4) is rejected. */
+ * morphocore/functional/merge_enum.py:4-11 sends through the operator schema. SMOOTH (4) is the merge of the
+ * mc_smorph_scm_* entry points only. */
 enum mc_merge { MC_MERGE_MAX = 0, MC_MERGE_MIN = 1, MC_MERGE_ADD = 2, MC_MERGE_AVERAGE = 3, MC_MERGE_SMOOTH = 4, MC_MERGE_IDENTITY = 5 };
 
 /* Padding family, MORPHO_PADDING_KIND (CPP/morpho_op_enum.hpp:41-45): out-of-image taps read `fill`
@@ -96,7 +97,8 @@ int mc_morpho_backward(const mc_desc* desc, const void* x, const void* w, const 
 int mc_morpho_backward_noalloc(const mc_desc* desc, const void* x, const void* w, const void* gy, void* gx, void* gw, void* stream);
 
 /* Forward smorph (alpha-softmax soft extremum) with the fused channel merge.
- * Replaces smorph_forward_cuda<T> (CU/smorph.cuh:15-18, CU/smorph.cu:52-61) for every merge but SMOOTH.
+ * Replaces smorph_forward_cuda<T> (CU/smorph.cuh:15-18, CU/smorph.cu:52-61) for every merge but SMOOTH
+ * (mc_smorph_scm_forward).
  * alpha_pairs holds one value per (o, i) pair, [Co, Ci] ([Co] for identity), as produced by
  * smorph_pair_alphas (CPP/smorph_cpu_kernels.hxx:643-649). `w` is the re-parametrised structuring element. */
 int mc_smorph_forward(const mc_desc* desc, const void* x, const void* w, const void* alpha_pairs, void* y, void* stream);
@@ -109,6 +111,23 @@ size_t mc_smorph_backward_workspace_bytes(const mc_desc* desc);
  * like alpha_pairs) are overwritten. */
 int mc_smorph_backward(const mc_desc* desc, const void* x, const void* w, const void* alpha_pairs, const void* y, const void* gy, void* gx,
                        void* gw, void* galpha_pairs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Smorph with the smooth channel merge ("Smorph SCM"): the Ci soft extrema c_i of an output pixel are merged by a
+ * second soft extremum, final = sum_i q_i c_i / sum_i q_i with q_i = exp(beta[o] (c_i - ref)), ref = max_i c_i for
+ * beta[o] >= 0 and min_i c_i otherwise (CPP/smorph_cpu_kernels.hxx:231-266).
+ * Replaces smorph_forward_cuda<T> called with MORPHO_MERGE::SMOOTH (CU/smorph.cuh:15-18, CPP/smorph_scm.cpp:13-56).
+ * desc->merge must be MC_MERGE_SMOOTH; alpha_pairs is [Co, Ci], beta [Co]. */
+int mc_smorph_scm_forward(const mc_desc* desc, const void* x, const void* w, const void* alpha_pairs, const void* beta, void* y, void* stream);
+
+/* Scratch bytes mc_smorph_scm_backward needs: ref and 1 / sum_i q_i of every output pixel. */
+size_t mc_smorph_scm_backward_workspace_bytes(const mc_desc* desc);
+
+/* Backward of mc_smorph_scm_forward. Replaces smorph_backward_cuda<T> called with MORPHO_MERGE::SMOOTH
+ * (CU/smorph.cuh:20-25, CPP/smorph_scm.cpp:58-96). y is the forward output. gx, gw, galpha_pairs ([Co, Ci]) and
+ * gbeta ([Co]) are overwritten. */
+int mc_smorph_scm_backward(const mc_desc* desc, const void* x, const void* w, const void* alpha_pairs, const void* beta, const void* y,
+                           const void* gy, void* gx, void* gw, void* galpha_pairs, void* gbeta, void* workspace, size_t workspace_bytes,
+                           void* stream);
 
 const char* mc_status_string(int status);
 const char* mc_last_error(void);

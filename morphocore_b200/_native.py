@@ -21,6 +21,7 @@ lib.mc_last_error.restype = ctypes.c_char_p
 lib.mc_launch_count.restype = ctypes.c_uint64
 lib.mc_morpho_backward_workspace_bytes.restype = ctypes.c_size_t
 lib.mc_smorph_backward_workspace_bytes.restype = ctypes.c_size_t
+lib.mc_smorph_scm_backward_workspace_bytes.restype = ctypes.c_size_t
 torch.ops.load_library(EXT_PATH)
 ops = torch.ops.morphocore
 

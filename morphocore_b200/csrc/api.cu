@@ -43,7 +43,7 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 /// Checks shared by every entry point. The limits on taps and channels are those of the packed winner
 /// index, (channel << 16) | tap.
-static int validate(const mc_desc* d, bool morph)
+static int validate(const mc_desc* d, bool morph, bool smooth = false)
 {
     if (d == nullptr) { set_last_error("descriptor is NULL"); return MC_ERR_INVALID_ARGUMENT; }
     if (d->B < 0 || d->Ci <= 0 || d->Co <= 0 || d->H < 0 || d->W < 0 || d->kH <= 0 || d->kW <= 0)
@@ -53,7 +53,12 @@ static int validate(const mc_desc* d, bool morph)
     }
     if (d->dtype != MC_F32 && d->dtype != MC_F64) { set_last_error("unknown dtype %d", d->dtype); return MC_ERR_INVALID_ARGUMENT; }
     if (d->merge < MC_MERGE_MAX || d->merge > MC_MERGE_IDENTITY) { set_last_error("Unknown merge mode %d", d->merge); return MC_ERR_INVALID_ARGUMENT; }
-    if (d->merge == MC_MERGE_SMOOTH) { set_last_error("the smooth channel merge is not implemented by these kernels"); return MC_ERR_UNSUPPORTED; }
+    if (smooth && d->merge != MC_MERGE_SMOOTH) { set_last_error("mc_smorph_scm_* take merge = MC_MERGE_SMOOTH"); return MC_ERR_INVALID_ARGUMENT; }
+    if (!smooth && d->merge == MC_MERGE_SMOOTH)
+    {
+        set_last_error("the smooth channel merge exists for smorph only and has its own entry points, mc_smorph_scm_*");
+        return MC_ERR_UNSUPPORTED;
+    }
     if (d->merge == MC_MERGE_IDENTITY && d->Co != d->Ci)
     {
         set_last_error("Identity mode requires weight.shape[0] == input.shape[1]");
@@ -191,6 +196,64 @@ int mc_smorph_backward(const mc_desc* desc, const void* x, const void* w, const 
     return smorph_backward<double>(*desc, static_cast<const double*>(x), static_cast<const double*>(w), static_cast<const double*>(alpha_pairs),
                                    static_cast<const double*>(y), static_cast<const double*>(gy), static_cast<double*>(gx), static_cast<double*>(gw),
                                    static_cast<double*>(galpha_pairs), workspace, s);
+}
+
+int mc_smorph_scm_forward(const mc_desc* desc, const void* x, const void* w, const void* alpha_pairs, const void* beta, void* y, void* stream)
+{
+    const int rc = validate(desc, false, true);
+    if (rc != MC_OK) return rc;
+    if (empty(desc)) return MC_OK;
+    MC_REQUIRE(x); MC_REQUIRE(w); MC_REQUIRE(alpha_pairs); MC_REQUIRE(beta); MC_REQUIRE(y);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == MC_F32)
+        return smorph_scm_forward<float>(*desc, static_cast<const float*>(x), static_cast<const float*>(w), static_cast<const float*>(alpha_pairs),
+                                         static_cast<const float*>(beta), static_cast<float*>(y), s);
+    return smorph_scm_forward<double>(*desc, static_cast<const double*>(x), static_cast<const double*>(w), static_cast<const double*>(alpha_pairs),
+                                      static_cast<const double*>(beta), static_cast<double*>(y), s);
+}
+
+size_t mc_smorph_scm_backward_workspace_bytes(const mc_desc* desc)
+{
+    if (desc == nullptr) return 0;
+    return 2 * (desc->dtype == MC_F32 ? 4 : 8) * static_cast<size_t>(desc->B) * desc->Co * desc->H * desc->W;
+}
+
+int mc_smorph_scm_backward(const mc_desc* desc, const void* x, const void* w, const void* alpha_pairs, const void* beta, const void* y,
+                           const void* gy, void* gx, void* gw, void* galpha_pairs, void* gbeta, void* workspace, size_t workspace_bytes,
+                           void* stream)
+{
+    const int rc = validate(desc, false, true);
+    if (rc != MC_OK) return rc;
+    MC_REQUIRE(gw); MC_REQUIRE(galpha_pairs); MC_REQUIRE(gbeta);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t esz = desc->dtype == MC_F32 ? 4 : 8;
+    if (empty(desc))
+    {
+        const size_t an = static_cast<size_t>(desc->Co) * desc->Ci;
+        if (cudaMemsetAsync(gw, 0, an * desc->kH * desc->kW * esz, s) != cudaSuccess || cudaMemsetAsync(galpha_pairs, 0, an * esz, s) != cudaSuccess
+            || cudaMemsetAsync(gbeta, 0, desc->Co * esz, s) != cudaSuccess)
+        {
+            set_last_error("cudaMemsetAsync failed");
+            return MC_ERR_CUDA;
+        }
+        return MC_OK;
+    }
+    MC_REQUIRE(x); MC_REQUIRE(w); MC_REQUIRE(alpha_pairs); MC_REQUIRE(beta); MC_REQUIRE(y); MC_REQUIRE(gy); MC_REQUIRE(gx);
+    const size_t need = mc_smorph_scm_backward_workspace_bytes(desc);
+    if (workspace == nullptr || workspace_bytes < need)
+    {
+        set_last_error("workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        return MC_ERR_WORKSPACE;
+    }
+    if (desc->dtype == MC_F32)
+        return smorph_scm_backward<float>(*desc, static_cast<const float*>(x), static_cast<const float*>(w), static_cast<const float*>(alpha_pairs),
+                                          static_cast<const float*>(beta), static_cast<const float*>(y), static_cast<const float*>(gy),
+                                          static_cast<float*>(gx), static_cast<float*>(gw), static_cast<float*>(galpha_pairs),
+                                          static_cast<float*>(gbeta), workspace, s);
+    return smorph_scm_backward<double>(*desc, static_cast<const double*>(x), static_cast<const double*>(w), static_cast<const double*>(alpha_pairs),
+                                       static_cast<const double*>(beta), static_cast<const double*>(y), static_cast<const double*>(gy),
+                                       static_cast<double*>(gx), static_cast<double*>(gw), static_cast<double*>(galpha_pairs),
+                                       static_cast<double*>(gbeta), workspace, s);
 }
 
 const char* mc_status_string(int status)

@@ -262,5 +262,8 @@ template <typename T> int morpho_backward(const mc_desc& d, const T* x, const T*
 template <typename T> int smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, T* y, T* counts, cudaStream_t stream);
 template <typename T> int smorph_backward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* y, const T* gy, T* gx, T* gw,
                                           T* galpha, void* ws, cudaStream_t stream);
+template <typename T> int smorph_scm_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* beta, T* y, cudaStream_t stream);
+template <typename T> int smorph_scm_backward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* beta, const T* y, const T* gy, T* gx,
+                                              T* gw, T* galpha, T* gbeta, void* ws, cudaStream_t stream);
 
 }  // namespace mc

@@ -553,6 +553,9 @@ struct SmorphForwardArgs
     T* y;             // output (normal mode)
     const T* target;  // forward output, stats mode
     T* counts;        // stats mode: channels within 1e-6 of the target, per output pixel
+    const T* beta;    // smooth merge: one value per output channel
+    T* soft_ref;      // smooth merge, backward's statistics pass: extremum of the channel outputs per output pixel (instead of y)
+    T* soft_inv;      // and 1 / sum_i q_i
     int merge;
     int o_groups;
     int chunk;
@@ -564,10 +567,16 @@ struct SmorphForwardArgs
 /// USE_TMA the windows of chunk n + 1 are copied by TMA while chunk n is computed, see morpho_forward_kernel.
 /// STATS: instead of the merged output, count for MAX / MIN merges the channels whose soft extremum is
 /// within 1e-6 of the merged value, which share the gradient (csrc/cpp/smorph_cpu_kernels.hxx:397-398, 507-519).
-template <typename T, int KW, int OB, bool STATS, bool USE_TMA>
+/// MODE 2 (smooth merge, Smorph SCM; csrc/cpp/smorph_cpu_kernels.hxx:231-266): the channel outputs c_i of an output
+/// pixel are merged by a second soft extremum with the output channel's beta, final = sum_i q_i c_i / sum_i q_i,
+/// q_i = exp(beta (c_i - ref)), ref = max_i c_i (beta >= 0) or min_i c_i. The channels stream through the CTA, so the
+/// sums are kept relative to the running extremum and rescaled when it moves. The kernel writes the merged value,
+/// or, for the backward pass, ref and 1 / sum_i q_i.
+template <typename T, int KW, int OB, int MODE, bool USE_TMA>
 __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     smorph_forward_kernel(const SmorphForwardArgs<T> a, const __grid_constant__ CUtensorMap tmap)
 {
+    constexpr bool STATS = MODE == 1, SOFT = MODE == 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const Geometry& g = a.g;
     const int taps = g.taps();
@@ -580,7 +589,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     T* sw = sx0 + (USE_TMA ? 2 : 1) * 2 * slot_elems;   // [2 chunk][taps][OB], sign folded
     T* sa = sw + 2 * a.chunk * taps * OB;                 // [2 chunk][OB][2]: sign, exp scale
     // Factorised path: [2 chunk][taps][OB] (Ew, Bw), [2 chunk][OB] (Mw, range of w), then one (E, A) buffer per warp.
-    constexpr bool FACTOR = can_factorise<T, KW, STATS>();
+    constexpr bool FACTOR = can_factorise<T, KW, MODE != 0>();
     float2* seb = reinterpret_cast<float2*>(smem_raw + (reinterpret_cast<unsigned char*>(sa + 2 * a.chunk * OB * 2) - smem_raw + 15) / 16 * 16);
     float2* spair = seb + 2 * a.chunk * taps * OB;
     float4* sea = reinterpret_cast<float4*>(smem_raw + (reinterpret_cast<unsigned char*>(spair + 2 * a.chunk * OB) - smem_raw + 15) / 16 * 16)
@@ -663,6 +672,27 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 }
             }
 
+    // Smooth merge: running extremum of sign(beta) c_i and sum of q_i per pixel (merged holds sum q_i c_i).
+    [[maybe_unused]] T soft_m[SOFT ? OB : 1][PATCH_H][PATCH_W], soft_s[SOFT ? OB : 1][PATCH_H][PATCH_W];
+    [[maybe_unused]] T soft_sign[OB], soft_scale[OB];
+    if constexpr (SOFT)
+    {
+#pragma unroll
+        for (int o = 0; o < OB; o++)
+        {
+            const T bt = o0 + o < g.Co ? __ldg(a.beta + o0 + o) : T(0);
+            soft_sign[o] = bt >= T(0) ? T(1) : T(-1);
+            soft_scale[o] = exp_scale(bt >= T(0) ? bt : -bt);
+#pragma unroll
+            for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                for (int j = 0; j < PATCH_W; j++)
+                {
+                    soft_m[o][rr][j] = -Limits<T>::inf();
+                    soft_s[o][rr][j] = T(0);
+                }
+        }
+    }
     [[maybe_unused]] T offset[OB];   // factorised path: per-channel constant part of the sum
 #pragma unroll
     for (int o = 0; o < OB; o++) offset[o] = T(0);
@@ -843,7 +873,22 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
 #pragma unroll
                         for (int j = 0; j < PATCH_W; j++) f(merged[o][rr][j], s * out[rr][j], target[o][rr][j]);
                 };
-                if constexpr (STATS)
+                if constexpr (SOFT)
+                {
+#pragma unroll
+                    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                        for (int j = 0; j < PATCH_W; j++)
+                        {
+                            const T c = s * out[rr][j], t = soft_sign[o] * c;
+                            const T top = soft_m[o][rr][j] < t ? t : soft_m[o][rr][j];
+                            const T keep = soft_exp(soft_m[o][rr][j] - top, soft_scale[o]), q = soft_exp(t - top, soft_scale[o]);
+                            soft_s[o][rr][j] = fma(soft_s[o][rr][j], keep, q);
+                            merged[o][rr][j] = fma(merged[o][rr][j], keep, q * c);
+                            soft_m[o][rr][j] = top;
+                        }
+                }
+                else if constexpr (STATS)
                     for_pixels([](T& m, T v, T t) {
                         const T dist = v - t;
                         if (dist < T(1e-6) && dist > -T(1e-6)) m += T(1);
@@ -868,16 +913,28 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 const int h = tile_h0 + ty * PATCH_H + rr, w = tile_w0 + tx * PATCH_W + j;
                 if (o0 + o >= g.Co || h >= g.H || w >= g.W) continue;
                 T v = merged[o][rr][j];
+                const int64_t at = ((static_cast<int64_t>(b) * g.Co + o0 + o) * g.H + h) * g.W + w;
+                if constexpr (SOFT)
+                {
+                    const T inv = T(1) / soft_s[o][rr][j];
+                    if (a.soft_ref != nullptr)
+                    {
+                        a.soft_ref[at] = soft_sign[o] * soft_m[o][rr][j];
+                        a.soft_inv[at] = inv;
+                    }
+                    else a.y[at] = v * inv;
+                    continue;
+                }
                 if constexpr (FACTOR) v += offset[o];
                 if (!STATS && a.merge == MC_MERGE_AVERAGE) v = v / divisor;
-                dst[((static_cast<int64_t>(b) * g.Co + o0 + o) * g.H + h) * g.W + w] = v;
+                dst[at] = v;
             }
 }
 
-template <typename T, int KW, int OB, bool STATS, bool USE_TMA>
+template <typename T, int KW, int OB, int MODE, bool USE_TMA>
 int launch_smorph_forward_variant(const SmorphForwardArgs<T>& a, const CUtensorMap& tmap, int64_t blocks, size_t smem, cudaStream_t stream)
 {
-    auto kernel = smorph_forward_kernel<T, KW, OB, STATS, USE_TMA>;
+    auto kernel = smorph_forward_kernel<T, KW, OB, MODE, USE_TMA>;
     if (!allow_shared(kernel, smem))
     {
         set_last_error("cannot opt in to %zu bytes of shared memory", smem);
@@ -888,12 +945,14 @@ int launch_smorph_forward_variant(const SmorphForwardArgs<T>& a, const CUtensorM
 }
 
 template <typename T, int KW, int OB>
-int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, T* y, const T* target, T* counts, cudaStream_t stream)
+int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, T* y, const T* target, T* counts, cudaStream_t stream,
+                          const T* beta = nullptr, T* soft_ref = nullptr, T* soft_inv = nullptr)
 {
     SmorphForwardArgs<T> a;
     a.g = make_geometry(d, sizeof(T));
     a.g.replicate = false;  // out-of-image taps are excluded, never read
     a.x = x; a.w = w; a.alpha = alpha; a.y = y; a.target = target; a.counts = counts; a.merge = d.merge;
+    a.beta = beta; a.soft_ref = soft_ref; a.soft_inv = soft_inv;
     a.o_groups = (d.Co + OB - 1) / OB;
     a.errors = device_error_counter();
     const int channels = a.g.identity ? 1 : d.Ci;
@@ -905,7 +964,8 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     // The factorised path suits merges without a winner test: MAX / MIN compare the recomputed soft extremum
     // with the stored output within 1e-6, which only the same arithmetic in every pass guarantees.
     constexpr bool FACTOR = can_factorise<T, KW, false>();
-    a.factorise = FACTOR && !stats && d.merge != MC_MERGE_MAX && d.merge != MC_MERGE_MIN;
+    const bool soft = d.merge == MC_MERGE_SMOOTH;
+    a.factorise = FACTOR && !stats && !soft && d.merge != MC_MERGE_MAX && d.merge != MC_MERGE_MIN;
     size_t small = 2 * (static_cast<size_t>(a.g.taps()) * OB + 2 * OB) * sizeof(T);  // up to two chunks of channels per stage
     size_t extra = 0;
     if (a.factorise)
@@ -927,8 +987,9 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     if (plan(2, chunk, smem) && make_window_tensor_map(&tmap, x, sizeof(T), d.B, d.Ci, d.H, d.W, a.g.win_stride, a.g.win_rows, chunk))
     {
         a.chunk = chunk;
-        return stats ? launch_smorph_forward_variant<T, KW, OB, true, true>(a, tmap, blocks, smem, stream)
-                     : launch_smorph_forward_variant<T, KW, OB, false, true>(a, tmap, blocks, smem, stream);
+        if (soft) return launch_smorph_forward_variant<T, KW, OB, 2, true>(a, tmap, blocks, smem, stream);
+        return stats ? launch_smorph_forward_variant<T, KW, OB, 1, true>(a, tmap, blocks, smem, stream)
+                     : launch_smorph_forward_variant<T, KW, OB, 0, true>(a, tmap, blocks, smem, stream);
     }
     if (!plan(1, chunk, smem))
     {
@@ -936,8 +997,9 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
         return MC_ERR_UNSUPPORTED;
     }
     a.chunk = chunk;
-    return stats ? launch_smorph_forward_variant<T, KW, OB, true, false>(a, tmap, blocks, smem, stream)
-                 : launch_smorph_forward_variant<T, KW, OB, false, false>(a, tmap, blocks, smem, stream);
+    if (soft) return launch_smorph_forward_variant<T, KW, OB, 2, false>(a, tmap, blocks, smem, stream);
+    return stats ? launch_smorph_forward_variant<T, KW, OB, 1, false>(a, tmap, blocks, smem, stream)
+                 : launch_smorph_forward_variant<T, KW, OB, 0, false>(a, tmap, blocks, smem, stream);
 }
 
 template <typename T>
@@ -954,6 +1016,10 @@ struct SmorphBackwardArgs
     T* gw;
     T* galpha;
     int merge;
+    const T* beta;      // smooth merge: one value per output channel
+    const T* soft_ref;  // smooth merge: extremum of the channel outputs per output pixel
+    const T* soft_inv;  // smooth merge: 1 / sum_i q_i per output pixel
+    T* gbeta;           // smooth merge: gradient of beta
     int o_chunk;      // output channels whose weights and bins are staged together
     T scale;          // 1 / Ci for AVERAGE
 };
@@ -1032,7 +1098,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     T* spar = sw + OC * taps;                  // [OC][3]: sign, |alpha|, exp scale
     T* wbins = spar + OC * 3;                  // [WARPS][OC][taps]
     T* abins = wbins + WARPS * OC * taps;      // [WARPS][OC]
-    T* red = abins + WARPS * OC + (threadIdx.x >> 5) * RED_ROWS * RED_STRIDE;  // this warp's reduction scratch
+    T* bbins = abins + WARPS * OC;             // [WARPS][OC]: gradient of beta (smooth merge)
+    T* red = bbins + WARPS * OC + (threadIdx.x >> 5) * RED_ROWS * RED_STRIDE;  // this warp's reduction scratch
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int ci = blockIdx.x % g.Ci;
@@ -1047,6 +1114,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     const int wci = g.identity ? 1 : g.Ci;
     const int wi = g.identity ? 0 : ci;
     const bool winner_takes_all = a.merge == MC_MERGE_MAX || a.merge == MC_MERGE_MIN;
+    const bool soft_merge = a.merge == MC_MERGE_SMOOTH;
     const int o_begin = g.identity ? ci : 0;
     const int o_end = g.identity ? ci + 1 : g.Co;
 
@@ -1105,7 +1173,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             const T v = __ldg(a.w + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps + k);
             sw[e] = al >= T(0) ? v : -v;
         }
-        for (int e = threadIdx.x; e < WARPS * OC * (taps + 1); e += THREADS) wbins[e] = T(0);  // bins of warps that skip stay zero
+        for (int e = threadIdx.x; e < WARPS * OC * (taps + 2); e += THREADS) wbins[e] = T(0);  // bins of warps that skip stay zero
         __syncthreads();
 
         if (warp_live)
@@ -1156,6 +1224,45 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
                         }
                 }
+                if (soft_merge)
+                {
+                    // Smooth merge: channel i receives g (p_i + beta p_i (c_i - final)), p_i = exp(beta (c_i - ref)) / sum_i q_i,
+                    // and beta receives sum_i p_i (c_i - ref) (c_i - final) g (csrc/cpp/smorph_cpu_kernels.hxx:478, 520-552).
+                    T out[PATCH_H][PATCH_W];
+                    if constexpr (KW == 3)
+                    {
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+                        {
+                            T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+                            smorph3_values(win, sw + oo * taps, 1, s, g, tx, ty, rr, d);
+                            smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+#pragma unroll
+                            for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
+                        }
+                    }
+                    else
+                    {
+                        T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
+                        smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
+                    }
+                    const T bt = __ldg(a.beta + o);
+                    T beta_sum = T(0);
+#pragma unroll
+                    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                        for (int j = 0; j < PATCH_W; j++)
+                        {
+                            if (!live[rr][j]) continue;
+                            const int64_t at = at0[rr] + static_cast<int64_t>(o) * plane + j;
+                            const T c = s * out[rr][j], ref = __ldg(a.soft_ref + at), final = __ldg(a.y + at);
+                            const T p = exp((c - ref) * bt) * __ldg(a.soft_inv + at);
+                            beta_sum = fma(p * (c - ref) * (c - final), grad[rr][j], beta_sum);
+                            grad[rr][j] = grad[rr][j] * fma(bt * p, c - final, p);
+                        }
+                    beta_sum = warp_sum(beta_sum);
+                    if (lane == 0) bbins[warp * OC + oo] = beta_sum;
+                }
                 if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
                 else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
 #pragma unroll
@@ -1179,6 +1286,13 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
 #pragma unroll
             for (int wp = 0; wp < WARPS; wp++) total += abins[wp * OC + oo];
             if (total != T(0)) atomic_add(a.galpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci), total);
+            if (soft_merge)
+            {
+                T beta_total = T(0);
+#pragma unroll
+                for (int wp = 0; wp < WARPS; wp++) beta_total += bbins[wp * OC + oo];
+                if (beta_total != T(0)) atomic_add(a.gbeta + oc0 + oo, beta_total);
+            }
         }
     }
 
@@ -1211,7 +1325,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
 
 template <typename T, int KH, int KW>
 int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* y, const T* counts, const T* gy, T* gx, T* gw,
-                           T* galpha, cudaStream_t stream)
+                           T* galpha, cudaStream_t stream, const T* beta = nullptr, const T* soft_ref = nullptr, const T* soft_inv = nullptr,
+                           T* gbeta = nullptr)
 {
     constexpr int WARPS = THREADS / 32;
     SmorphBackwardArgs<T> a;
@@ -1219,10 +1334,11 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     a.g.replicate = false;  // out-of-image taps are excluded, never read
     a.x = x; a.w = w; a.alpha = alpha; a.y = y; a.counts = counts; a.gy = gy; a.gx = gx; a.gw = gw; a.galpha = galpha;
     a.merge = d.merge;
+    a.beta = beta; a.soft_ref = soft_ref; a.soft_inv = soft_inv; a.gbeta = gbeta;
     a.scale = d.merge == MC_MERGE_AVERAGE ? T(1.0) / static_cast<T>(d.Ci) : T(1.0);
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
     const size_t fixed = (3 * static_cast<size_t>(a.g.window_elems()) + WARPS * RED_ROWS * RED_STRIDE) * sizeof(T);
-    const size_t per_o = (taps + 3 + WARPS * (taps + 1)) * sizeof(T);
+    const size_t per_o = (taps + 3 + WARPS * (taps + 2)) * sizeof(T);
     if (fixed + per_o > MAX_SHARED_BYTES)
     {
         set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);

@@ -65,4 +65,53 @@ int smorph_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const 
     });
 }
 
+/// Forward launch of the smooth merge: the merged output, or (soft_ref != nullptr) the per-pixel statistics.
+template <typename T>
+static int launch_scm_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, const T* beta, T* y, T* soft_ref, T* soft_inv,
+                              cudaStream_t stream)
+{
+    return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
+        constexpr int KW = decltype(kw)::value;
+        return d.Co >= 2 ? launch_smorph_forward<T, KW, 2>(d, x, w, alpha, y, nullptr, nullptr, stream, beta, soft_ref, soft_inv)
+                         : launch_smorph_forward<T, KW, 1>(d, x, w, alpha, y, nullptr, nullptr, stream, beta, soft_ref, soft_inv);
+    });
+}
+
+template <>
+int smorph_scm_forward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const MC_T* alpha, const MC_T* beta, MC_T* y, cudaStream_t stream)
+{
+    return launch_scm_forward<MC_T>(d, x, w, alpha, beta, y, nullptr, nullptr, stream);
+}
+
+template <>
+int smorph_scm_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const MC_T* alpha, const MC_T* beta, const MC_T* y, const MC_T* gy,
+                              MC_T* gx, MC_T* gw, MC_T* galpha, MC_T* gbeta, void* ws, cudaStream_t stream)
+{
+    using T = MC_T;
+    const size_t taps = static_cast<size_t>(d.kH) * d.kW, pixels = static_cast<size_t>(d.B) * d.Co * d.H * d.W;
+    if (cudaMemsetAsync(gx, 0, sizeof(T) * static_cast<size_t>(d.B) * d.Ci * d.H * d.W, stream) != cudaSuccess
+        || cudaMemsetAsync(gw, 0, sizeof(T) * d.Co * d.Ci * taps, stream) != cudaSuccess
+        || cudaMemsetAsync(galpha, 0, sizeof(T) * d.Co * d.Ci, stream) != cudaSuccess
+        || cudaMemsetAsync(gbeta, 0, sizeof(T) * d.Co, stream) != cudaSuccess)
+    {
+        set_last_error("cudaMemsetAsync: %s", cudaGetErrorString(cudaGetLastError()));
+        return MC_ERR_CUDA;
+    }
+    // One more pass over every channel for the extremum and the sum of the channel weights of each output pixel.
+    T* soft_ref = static_cast<T*>(ws);
+    T* soft_inv = soft_ref + pixels;
+    const int rc = launch_scm_forward<T>(d, x, w, alpha, beta, nullptr, soft_ref, soft_inv, stream);
+    if (rc != MC_OK) return rc;
+    if (sizeof(T) == 4 && d.kH == d.kW)
+    {
+        if (d.kW == 3) return launch_smorph_backward<T, 3, 3>(d, x, w, alpha, y, nullptr, gy, gx, gw, galpha, stream, beta, soft_ref, soft_inv, gbeta);
+        if (d.kW == 5) return launch_smorph_backward<T, 5, 5>(d, x, w, alpha, y, nullptr, gy, gx, gw, galpha, stream, beta, soft_ref, soft_inv, gbeta);
+        if (d.kW == 7) return launch_smorph_backward<T, 7, 7>(d, x, w, alpha, y, nullptr, gy, gx, gw, galpha, stream, beta, soft_ref, soft_inv, gbeta);
+    }
+    return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
+        constexpr int KW = decltype(kw)::value;
+        return launch_smorph_backward<T, 0, KW>(d, x, w, alpha, y, nullptr, gy, gx, gw, galpha, stream, beta, soft_ref, soft_inv, gbeta);
+    });
+}
+
 }  // namespace mc

@@ -276,6 +276,78 @@ public:
     }
 };
 
+/// Smorph with the smooth channel merge, the autograd function of torch.ops.morphocore.smorph_scm
+/// (reference: csrc/cpp/smorph_scm.cpp:13-96). beta holds one value per output channel.
+class SmorphScmFunction : public torch::autograd::Function<SmorphScmFunction>
+{
+public:
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input, torch::Tensor weight, torch::Tensor alpha,
+                                 torch::Tensor beta)
+    {
+        const int64_t original_dims = input.dim();
+        torch::Tensor input4d = input_to_4d(input);
+        torch::Tensor weight4d = weight_to_4d(weight);
+        require_cuda(input, "input");
+        require_cuda(weight, "weight");
+        require_cuda(alpha, "alpha");
+        require_cuda(beta, "beta");
+        TORCH_CHECK(input.scalar_type() == weight.scalar_type() && input.scalar_type() == alpha.scalar_type()
+                        && input.scalar_type() == beta.scalar_type(),
+                    "input, weight, alpha and beta must have the same dtype");
+        TORCH_CHECK(input4d.size(1) == weight4d.size(1), "Input channels must match weight input channels");
+        TORCH_CHECK(beta.numel() == weight4d.size(0), "Beta must have shape [out_channels]");
+        const c10::cuda::CUDAGuard device_guard(input.device());
+        input4d = input4d.contiguous();
+        weight4d = weight4d.contiguous();
+        const torch::Tensor alphas = pair_alphas(alpha, MC_MERGE_SMOOTH, weight4d.size(0), input4d.size(1));
+        const torch::Tensor betas = beta.contiguous();
+
+        const mc_desc d = make_desc(input4d, weight4d, MC_OP_DILATION, MC_MERGE_SMOOTH);
+        torch::Tensor output = torch::empty({input4d.size(0), weight4d.size(0), input4d.size(2), input4d.size(3)}, input4d.options());
+        check_status(mc_smorph_scm_forward(&d, input4d.data_ptr(), weight4d.data_ptr(), alphas.data_ptr(), betas.data_ptr(), output.data_ptr(),
+                                           at::cuda::getCurrentCUDAStream().stream()));
+        // The backward pass reads the 4-D output: the final value of the soft merge.
+        ctx->save_for_backward({output, alpha, betas, input4d, weight4d});
+        ctx->saved_data["input_dims"] = original_dims;
+        ctx->saved_data["weight_dims"] = weight.dim();
+        return output_to_original(output, original_dims);
+    }
+
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grad_outputs)
+    {
+        const auto saved = ctx->get_saved_variables();
+        const torch::Tensor& output = saved[0];
+        const torch::Tensor& alpha = saved[1];
+        const torch::Tensor& beta = saved[2];
+        const torch::Tensor& input = saved[3];
+        const torch::Tensor& weight = saved[4];
+        torch::Tensor grad_output = input_to_4d(grad_outputs[0]).contiguous();
+        TORCH_CHECK(grad_output.sizes() == output.sizes(), "grad_output shape mismatch: expected [", output.sizes(), "] but got [",
+                    grad_output.sizes(), "]");
+        TORCH_CHECK(grad_output.scalar_type() == input.scalar_type(), "grad_output must have the same dtype as input");
+
+        const c10::cuda::CUDAGuard device_guard(input.device());
+        const mc_desc d = make_desc(input, weight, MC_OP_DILATION, MC_MERGE_SMOOTH);
+        const torch::Tensor alphas = pair_alphas(alpha, MC_MERGE_SMOOTH, weight.size(0), input.size(1));
+        torch::Tensor grad_input = torch::empty_like(input);
+        torch::Tensor grad_weight = torch::empty_like(weight);
+        torch::Tensor grad_alpha_pairs = torch::empty_like(alphas);
+        torch::Tensor grad_beta = torch::empty_like(beta);
+        const size_t ws_bytes = mc_smorph_scm_backward_workspace_bytes(&d);
+        torch::Tensor workspace = torch::empty({static_cast<int64_t>(ws_bytes)}, input.options().dtype(torch::kByte));
+        check_status(mc_smorph_scm_backward(&d, input.data_ptr(), weight.data_ptr(), alphas.data_ptr(), beta.data_ptr(), output.data_ptr(),
+                                            grad_output.data_ptr(), grad_input.data_ptr(), grad_weight.data_ptr(), grad_alpha_pairs.data_ptr(),
+                                            grad_beta.data_ptr(), workspace.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream()));
+
+        // A single alpha shared by every pair receives the gradient of all of them (csrc/cpp/smorph_scm.cpp:81-83).
+        torch::Tensor grad_alpha =
+            alpha.numel() == grad_alpha_pairs.numel() ? grad_alpha_pairs.view_as(alpha) : grad_alpha_pairs.sum().view_as(alpha);
+        grad_input = output_to_original(grad_input, ctx->saved_data["input_dims"].toInt());
+        if (ctx->saved_data["weight_dims"].toInt() == 2) grad_weight = grad_weight.squeeze(0).squeeze(0);
+        return {grad_input, grad_weight, grad_alpha, grad_beta};
+    }
+};
+
 int64_t checked_merge(int64_t merge)
 {
     TORCH_CHECK(merge >= 0 && merge <= MC_MERGE_IDENTITY, "Unknown merge mode ", merge);
@@ -309,9 +381,9 @@ torch::Tensor smorph(torch::Tensor input, torch::Tensor weight, torch::Tensor al
     return SmorphFunction::apply(input, weight, alpha, merge);
 }
 
-torch::Tensor smorph_scm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor)
+torch::Tensor smorph_scm(torch::Tensor input, torch::Tensor weight, torch::Tensor alpha, torch::Tensor beta)
 {
-    TORCH_CHECK(false, "smorph_scm (smooth channel merge with beta) is not implemented by morphocore_b200");
+    return SmorphScmFunction::apply(input, weight, alpha, beta);
 }
 
 }  // namespace

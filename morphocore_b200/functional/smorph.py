@@ -19,7 +19,9 @@ def smorph(x: torch.Tensor, w: torch.Tensor, alpha: torch.Tensor, beta: torch.Te
 
     x : (N, C_in, H, W); w : (C_out, C_in, K_h, K_w) ((C, 1, K_h, K_w) for 'identity').
     alpha : (C_out, C_in) ((C,) or (C, 1) for 'identity'), or a single value shared by every pair.
-    beta : selective channel merging (smooth merge); not implemented by these kernels.
+    beta : (C_out,), optional. When given, the channels are merged by a second soft extremum instead of
+        `channel_merge_mode` (Smorph SCM, `torch.ops.morphocore.smorph_scm`): with c_i the soft extremum of channel
+        i, out = sum_i softmax_i(beta c_i) c_i (reference: morphocore/functional/csrc/cpp/smorph_scm.cpp:13-56).
     channel_merge_mode : 'sum', 'max', 'min', 'mean' or 'identity'.
     """
     if channel_merge_mode == 'identity' or alpha.dim() == 1:

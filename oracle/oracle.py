@@ -137,3 +137,31 @@ def smorph_weight(w, alpha, merge="sum"):
     t = np.tanh(alpha)
     t = t.reshape(-1, 1, 1, 1) if (merge == "identity" or alpha.ndim == 1) else t[..., None, None]
     return (t * ((1 - t) / 2 * w[..., ::-1, ::-1] + (1 + t) / 2 * w)).astype(w.dtype)
+
+
+def smorph_scm_forward(x, w, alpha, beta):
+    """Smorph with the smooth channel merge: `w` is the re-parametrised structuring element, alpha one value per
+    pair (or a single value), beta one value per output channel."""
+    x = np.ascontiguousarray(x)
+    w = np.ascontiguousarray(w, dtype=x.dtype)
+    d = _desc("dilation", x, w, "sum")
+    a = pair_alphas(alpha, d.Co, d.Ci, "sum", x.dtype)
+    bt = np.ascontiguousarray(np.asarray(beta, dtype=x.dtype).reshape(-1))
+    assert bt.size == d.Co, "beta must have one value per output channel"
+    y = np.empty((d.B, d.Co, d.H, d.W), dtype=x.dtype)
+    getattr(lib(), "orc_smorph_scm_forward" + _suffix(x))(ctypes.byref(d), _p(x), _p(w), _p(a), _p(bt), _p(y))
+    return y
+
+
+def smorph_scm_backward(x, w, alpha, beta, gy):
+    """Returns (grad_input, grad_weight, grad_alpha_pairs, grad_beta)."""
+    x = np.ascontiguousarray(x)
+    w = np.ascontiguousarray(w, dtype=x.dtype)
+    gy = np.ascontiguousarray(gy, dtype=x.dtype)
+    d = _desc("dilation", x, w, "sum")
+    a = pair_alphas(alpha, d.Co, d.Ci, "sum", x.dtype)
+    bt = np.ascontiguousarray(np.asarray(beta, dtype=x.dtype).reshape(-1))
+    assert bt.size == d.Co, "beta must have one value per output channel"
+    gx, gw, ga, gb = np.empty_like(x), np.empty_like(w), np.empty_like(a), np.empty_like(bt)
+    getattr(lib(), "orc_smorph_scm_backward" + _suffix(x))(ctypes.byref(d), _p(x), _p(w), _p(a), _p(bt), _p(gy), _p(gx), _p(gw), _p(ga), _p(gb))
+    return gx, gw, ga, gb

@@ -41,3 +41,11 @@ def smorph(x, w, alpha, merge="sum"):
     t = t.view(-1, 1, 1, 1) if (merge == "identity" or alpha.dim() == 1) else t.unsqueeze(-1).unsqueeze(-1)
     w_tilde = t * ((1 - t) / 2 * w.flip(dims=(-2, -1)) + (1 + t) / 2 * w)
     return load().smorph(x, w_tilde, alpha, MERGES[merge])
+
+
+def smorph_scm(x, w, alpha, beta):
+    """Smooth channel merge: beta holds one value per output channel (morphocore/functional/smorph.py:72-73)."""
+    t = torch.tanh(alpha)
+    t = t.view(-1, 1, 1, 1) if alpha.dim() == 1 else t.unsqueeze(-1).unsqueeze(-1)
+    w_tilde = t * ((1 - t) / 2 * w.flip(dims=(-2, -1)) + (1 + t) / 2 * w)
+    return load().smorph_scm(x, w_tilde, alpha, beta)

@@ -7,7 +7,7 @@ import torch
 
 from morphocore_b200 import _native
 
-MERGES = {"max": 0, "min": 1, "sum": 2, "mean": 3, "identity": 5}
+MERGES = {"max": 0, "min": 1, "sum": 2, "mean": 3, "smooth": 4, "identity": 5}
 
 
 class Desc(ctypes.Structure):
@@ -90,3 +90,22 @@ def smorph_backward(x, w, alpha, y, gy, merge="sum"):
     check(lib.mc_smorph_backward(ctypes.byref(d), ptr(x), ptr(w), ptr(a), ptr(y), ptr(gy), ptr(gx), ptr(gw), ptr(ga), ptr(ws),
                                  ctypes.c_size_t(need), stream()))
     return gx, gw, ga
+
+
+def smorph_scm_forward(x, w, alpha, beta):
+    d = make_desc("dilation", x, w, "smooth")
+    a = pair_alphas(alpha, d.Co, d.Ci, "sum")
+    y = torch.empty((d.B, d.Co, d.H, d.W), dtype=x.dtype, device=x.device)
+    check(lib.mc_smorph_scm_forward(ctypes.byref(d), ptr(x), ptr(w), ptr(a), ptr(beta), ptr(y), stream()))
+    return y
+
+
+def smorph_scm_backward(x, w, alpha, beta, y, gy):
+    d = make_desc("dilation", x, w, "smooth")
+    a = pair_alphas(alpha, d.Co, d.Ci, "sum")
+    gx, gw, ga, gb = torch.empty_like(x), torch.empty_like(w), torch.empty_like(a), torch.empty_like(beta)
+    need = lib.mc_smorph_scm_backward_workspace_bytes(ctypes.byref(d))
+    ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib.mc_smorph_scm_backward(ctypes.byref(d), ptr(x), ptr(w), ptr(a), ptr(beta), ptr(y), ptr(gy), ptr(gx), ptr(gw), ptr(ga), ptr(gb),
+                                     ptr(ws), ctypes.c_size_t(need), stream()))
+    return gx, gw, ga, gb

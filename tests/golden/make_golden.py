@@ -4,6 +4,7 @@ Run once, in a process of its own, where the reference sources are available:
 
     python oracle/build_ref.py          # compiles the reference's CPU code into oracle/_ref/_C.so
     python tests/golden/make_golden.py  # writes tests/golden/*.npz and manifest.json
+    python tests/golden/make_golden.py scm_small   # only the named sets
 
 Every fixture stores the inputs next to the reference's outputs, so the tests need neither the
 reference nor a particular RNG. Full-size benchmark configurations are too large to store: for those
@@ -105,6 +106,33 @@ def smorph_cases():
     return arrays, manifest
 
 
+def scm_cases():
+    """Smorph with the smooth channel merge (beta per output channel): the reference has no test of its own for
+    it, so these outputs of its CPU operator are the only pin."""
+    arrays, manifest = {}, []
+    gen = torch.Generator().manual_seed(2468)
+    betas = (-50.0, -3.0, -0.2, 0.0, 0.7, 4.0, 60.0)
+    alphas = (-8.0, -1.0, 0.0, 2.0, 8.0)
+    for n, b0 in enumerate(betas):
+        B, Ci, Co, H, W, kH, kW = SHAPES[n % len(SHAPES)]
+        dtype = torch.float32 if n % 2 == 0 else torch.float64
+        a0 = alphas[n % len(alphas)]
+        x = torch.randn((B, Ci, H, W), generator=gen, dtype=dtype)
+        w = torch.randn((Co, Ci, kH, kW), generator=gen, dtype=dtype) * 0.5
+        alpha = torch.tensor([a0], dtype=dtype) if n % 3 == 2 else a0 + 0.5 * torch.randn((Co, Ci), generator=gen, dtype=dtype)
+        beta = b0 + 0.1 * torch.randn((Co,), generator=gen, dtype=dtype)
+        gy = torch.randn((B, Co, H, W), generator=gen, dtype=dtype)
+        xr, wr, ar, br = (t.clone().requires_grad_(True) for t in (x, w, alpha, beta))
+        y = R.smorph_scm(xr, wr, ar, br)
+        y.backward(gy)
+        key = f"c{n}"
+        for name, a in (("x", x), ("w", w), ("alpha", alpha), ("beta", beta), ("gy", gy), ("y", y.detach()), ("gx", xr.grad), ("gw", wr.grad),
+                        ("galpha", ar.grad), ("gbeta", br.grad)):
+            arrays[f"{key}_{name}"] = a.numpy()
+        manifest.append(dict(key=key, alpha0=a0, beta0=b0, dtype=str(dtype).split(".")[1]))
+    return arrays, manifest
+
+
 def sha(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
@@ -196,11 +224,18 @@ def full_size_cases():
 
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
+    # Without arguments every set is regenerated; otherwise only the named ones (the manifest keeps the others).
+    manifest_path = os.path.join(HERE, "manifest.json")
     out = {}
-    for name, fn in (("morph_small", morph_cases), ("smorph_small", smorph_cases), ("full_size", full_size_cases)):
+    if len(sys.argv) > 1 and os.path.exists(manifest_path):
+        with open(manifest_path) as f:
+            out = json.load(f)
+    for name, fn in (("morph_small", morph_cases), ("smorph_small", smorph_cases), ("scm_small", scm_cases), ("full_size", full_size_cases)):
+        if len(sys.argv) > 1 and name not in sys.argv[1:]:
+            continue
         arrays, manifest = fn()
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
         out[name] = manifest
         print(name, len(manifest), "cases", os.path.getsize(os.path.join(HERE, name + ".npz")) // 1024, "KiB", flush=True)
-    with open(os.path.join(HERE, "manifest.json"), "w") as f:
+    with open(manifest_path, "w") as f:
         json.dump(out, f, indent=1)

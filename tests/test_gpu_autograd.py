@@ -72,6 +72,34 @@ def test_gradcheck_smorph(F, merge, alpha0):
         assert torch.autograd.gradcheck(lambda p, q, r: F.smorph(p, q, r, channel_merge_mode=merge), (x, w, scalar), eps=1e-6, atol=1e-5)
 
 
+def test_smorph_scm_matches_golden_and_gradcheck(F, manifest, golden):
+    """functional.smorph with beta (smooth channel merge) against the reference CPU operator's outputs and gradients,
+    then a double-precision gradcheck of all four inputs."""
+    data = golden("scm_small")
+    for case in manifest["scm_small"]:
+        k = case["key"]
+        x, w, a, b = (torch.from_numpy(data[k + n]).cuda().requires_grad_(True) for n in ("_x", "_w", "_alpha", "_beta"))
+        y = F.smorph(x, w, a, beta=b)
+        y.backward(torch.from_numpy(data[k + "_gy"]).cuda())
+        f32 = x.dtype == torch.float32
+        big = abs(case["beta0"]) >= 50
+        tol = dict(rtol=1e-3 if big else 1e-4, atol=(3e-3 if big else 3e-4)) if f32 else dict(rtol=1e-8, atol=1e-9)
+        np.testing.assert_allclose(y.detach().cpu().numpy(), data[k + "_y"], rtol=1e-4 if f32 else 1e-10, atol=1e-5 if f32 else 1e-11, err_msg=str(case))
+        for name, t in (("gx", x), ("gw", w), ("galpha", a), ("gbeta", b)):
+            want = data[k + "_" + name]
+            np.testing.assert_allclose(t.grad.cpu().numpy(), want, rtol=tol["rtol"], atol=tol["atol"] * max(1.0, float(np.abs(want).max())),
+                                       err_msg=f"{case} {name}")
+    torch.manual_seed(5)
+    x = torch.randn(1, 3, 5, 6, dtype=torch.float64, device="cuda", requires_grad=True)
+    w = torch.randn(2, 3, 3, 3, dtype=torch.float64, device="cuda", requires_grad=True)
+    a = torch.randn(2, 3, dtype=torch.float64, device="cuda", requires_grad=True)
+    for b0 in (-2.0, 0.0, 1.5):
+        b = (b0 + 0.1 * torch.randn(2, dtype=torch.float64, device="cuda")).requires_grad_(True)
+        assert torch.autograd.gradcheck(lambda p, q, r, t: F.smorph(p, q, r, beta=t), (x, w, a, b), eps=1e-6, atol=1e-5)
+    with pytest.raises(RuntimeError, match="Beta must have shape"):
+        F.smorph(x, w, a, beta=torch.zeros(3, dtype=torch.float64, device="cuda"))
+
+
 def test_lower_dimensional_inputs(F):
     x2 = torch.randn(9, 8, device="cuda", requires_grad=True)
     w2 = torch.randn(3, 3, device="cuda", requires_grad=True)

@@ -234,6 +234,76 @@ def entry(manifest, key):
     return next(m for m in manifest["full_size"] if m["key"] == key)
 
 
+@pytest.mark.parametrize("case", [
+    # kernel, image, alphas, spread of x
+    (3, 224, "uniform", 1.0), (3, 97, "per_pair", 1.0), (3, 61, "extreme", 1.0), (3, 130, "per_pair", 30.0),
+    (5, 128, "per_pair", 1.0), (7, 128, "uniform_negative", 1.0), (7, 70, "extreme", 3.0)])
+@pytest.mark.parametrize("merge", ["sum", "mean", "identity"])
+def test_smorph_factorised_forward_matches_double(C, case, merge):
+    """The float forward pass of the sum / mean / identity merges replaces exp(|alpha| (u_k - ref)) by the product of a
+    per-pixel and a per-tap factor wherever |alpha| * (range of x in a warp's block + range of w) allows it, and
+    falls back to the max-subtracting form elsewhere (large |alpha|, wide-spread inputs). Both must agree with the
+    double kernel, which always subtracts the maximum: partial tiles, borders, alpha = 0, signs mixed within one
+    output channel, and ranges on both sides of the switch."""
+    k, hw, kind, spread = case
+    g = torch.Generator().manual_seed(1234 + k + hw)
+    co, ci = (6, 6) if merge == "identity" else (6, 5)
+    x = (spread * torch.randn((2, ci, hw, hw + 3), generator=g)).cuda()
+    w = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, k, k), generator=g)).cuda()
+    pairs = (co,) if merge == "identity" else (co, ci)
+    if kind == "uniform":
+        a = torch.full(pairs, 2.0)
+    elif kind == "uniform_negative":
+        a = torch.full(pairs, -8.0)
+    elif kind == "per_pair":
+        a = 3.0 * torch.randn(pairs, generator=g)
+    else:
+        values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, 1e-4, 3.0, 25.0, 400.0])
+        a = values[torch.randint(0, len(values), pairs, generator=g)]
+    a = a.cuda()
+    y = C.smorph_forward(x, w, a, merge)
+    ref = C.smorph_forward(x.double(), w.double(), a.double(), merge)
+    assert torch.isfinite(y).all()
+    # rtol 1e-4 / atol 1e-5 per channel output (the bar of the other float smorph tests), scaled by the number of
+    # channels a sum adds up
+    scale = ci if merge == "sum" else 1
+    torch.testing.assert_close(y.double(), ref, rtol=1e-4, atol=1e-5 * scale * max(1.0, spread))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("k", [3, 5, (4, 3), 11])
+def test_smorph_scm_against_oracle(C, k, dtype):
+    """Smorph with the smooth channel merge through the C-ABI: output, the four gradients, partial tiles, betas of
+    both signs, zero and large."""
+    kh, kw = (k, k) if isinstance(k, int) else k
+    rng = np.random.default_rng(77 + kh * kw)
+    B, Ci, Co, H, W = 2, 5, 4, 37, 70
+    x = rng.standard_normal((B, Ci, H, W)).astype(dtype)
+    wt = (0.4 * rng.standard_normal((Co, Ci, kh, kw))).astype(dtype)
+    alpha = (2.0 * rng.standard_normal((Co, Ci))).astype(dtype)
+    beta = np.array([-20.0, -0.7, 0.0, 3.0], dtype=dtype)
+    gy = rng.standard_normal((B, Co, H, W)).astype(dtype)
+    want_y = O.smorph_scm_forward(x, wt, alpha, beta)
+    want = O.smorph_scm_backward(x, wt, alpha, beta, gy)
+    xs, ws, al, bt, gs = (torch.from_numpy(t).cuda() for t in (x, wt, alpha, beta, gy))
+    y = C.smorph_scm_forward(xs, ws, al, bt)
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == np.float32 else dict(rtol=1e-10, atol=1e-11)
+    np.testing.assert_allclose(y.cpu().numpy(), want_y, **tol)
+    got = C.smorph_scm_backward(xs, ws, al, bt, y, gs)
+    gtol = dict(rtol=2e-3, atol=2e-3) if dtype == np.float32 else dict(rtol=1e-8, atol=1e-9)
+    for name, a, b in zip(("gx", "gw", "galpha", "gbeta"), got, want):
+        scale = max(1.0, float(np.abs(b).max()))
+        np.testing.assert_allclose(a.cpu().numpy().reshape(b.shape), b, rtol=gtol["rtol"], atol=gtol["atol"] * scale, err_msg=name)
+
+
+def test_smorph_scm_rejects_other_merges(C):
+    x = torch.randn(1, 2, 8, 8, device="cuda")
+    w = torch.randn(2, 2, 3, 3, device="cuda")
+    a = torch.zeros(2, 2, device="cuda")
+    with pytest.raises(RuntimeError, match="mc_smorph_scm"):
+        C.smorph_forward(x, w, a, "smooth")
+
+
 def test_cfg1_full_size_bit_exact(C, manifest):
     c = WL.cfg1()
     y = C.morpho_forward("dilation", c["x"].cuda(), c["w"].cuda(), "max", "replicate")

@@ -71,7 +71,7 @@ def test_cpu_tensors_are_rejected_loudly():
             call()
     with pytest.raises(RuntimeError, match="noise_scale"):
         F.dilation(x, w, noise_scale=-1.0, training=True)
-    with pytest.raises(RuntimeError, match="not implemented"):
+    with pytest.raises(RuntimeError, match="no CPU path"):
         F.smorph(x, w, torch.zeros(1, 1), beta=torch.zeros(1))
 
 
