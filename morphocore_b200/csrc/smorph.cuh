@@ -1082,7 +1082,8 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
 /// CTA = (batch element, input channel, tile), looping over the output channels in chunks: the sign-folded
 /// structuring elements and the per-warp gradient bins of a whole chunk live in shared memory, so the loop
 /// over the chunk's output channels runs without a barrier.
-template <typename T, int KH, int KW>
+/// SOFT: the smooth channel merge (its own instantiation, so that the other merges keep their register allocation).
+template <typename T, int KH, int KW, bool SOFT>
 __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) smorph_backward_kernel(const SmorphBackwardArgs<T> a)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -1114,7 +1115,6 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     const int wci = g.identity ? 1 : g.Ci;
     const int wi = g.identity ? 0 : ci;
     const bool winner_takes_all = a.merge == MC_MERGE_MAX || a.merge == MC_MERGE_MIN;
-    const bool soft_merge = a.merge == MC_MERGE_SMOOTH;
     const int o_begin = g.identity ? ci : 0;
     const int o_end = g.identity ? ci + 1 : g.Co;
 
@@ -1224,7 +1224,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
                         }
                 }
-                if (soft_merge)
+                if constexpr (SOFT)
                 {
                     // Smooth merge: channel i receives g (p_i + beta p_i (c_i - final)), p_i = exp(beta (c_i - ref)) / sum_i q_i,
                     // and beta receives sum_i p_i (c_i - ref) (c_i - final) g (csrc/cpp/smorph_cpu_kernels.hxx:478, 520-552).
@@ -1286,7 +1286,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
 #pragma unroll
             for (int wp = 0; wp < WARPS; wp++) total += abins[wp * OC + oo];
             if (total != T(0)) atomic_add(a.galpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci), total);
-            if (soft_merge)
+            if constexpr (SOFT)
             {
                 T beta_total = T(0);
 #pragma unroll
@@ -1352,10 +1352,13 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     const size_t smem = fixed + per_o * chunk;
     const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * d.Ci * d.B;
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
-    auto kernel = smorph_backward_kernel<T, KH, KW>;
-    if (!allow_shared(kernel, smem)) { set_last_error("cannot opt in to %zu bytes of shared memory", smem); return MC_ERR_UNSUPPORTED; }
-    kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a);
-    return check_launch("smorph_backward_kernel");
+    auto launch = [&](auto kernel) {
+        if (!allow_shared(kernel, smem)) { set_last_error("cannot opt in to %zu bytes of shared memory", smem); return static_cast<int>(MC_ERR_UNSUPPORTED); }
+        kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a);
+        return check_launch("smorph_backward_kernel");
+    };
+    if (d.merge == MC_MERGE_SMOOTH) return launch(smorph_backward_kernel<T, KH, KW, true>);
+    return launch(smorph_backward_kernel<T, KH, KW, false>);
 }
 
 }  // namespace mc
