@@ -315,17 +315,33 @@ struct FactorLayout
     static_assert(WS % 4 == 0 && HALF % 2 == 0 && 2 * (8 + HALF) >= WS, "the two copies cover the row");
 };
 
-/// Smallest and largest in-image x of the warp's block (window elements outside the image hold +-1e30).
+/// Signed integers that sort like the floats they are made from (and back).
+__device__ __forceinline__ int to_ordered(float v)
+{
+    const int i = __float_as_int(v);
+    return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float from_ordered(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
+
+/// Smallest and largest in-image x of the warp's block (window elements outside the image hold +-1e30 and are
+/// masked out; a block that lies inside the image, `inside`, has none and skips the masks).
 /// Lanes 0 .. 3 VECS - 1 each own one vector column of every third row.
 template <int KW>
-__device__ __forceinline__ void factor_range(const float* __restrict__ origin, int lane, float& lo, float& hi)
+__device__ __forceinline__ void factor_range(const float* __restrict__ origin, int lane, float& lo, float& hi, bool inside = false)
 {
     using L = FactorLayout<KW>;
     static_assert(3 * L::VECS <= 32, "three rows per sweep");
     lo = Limits<float>::inf();
     hi = -Limits<float>::inf();
     const int r0 = lane / L::VECS, c = lane - r0 * L::VECS;
-    if (r0 < 3)
+    if (r0 < 3 && inside)
+        for (int r = r0; r < L::ROWS; r += 3)
+        {
+            const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
+            lo = fminf(fminf(lo, v.x), fminf(v.y, fminf(v.z, v.w)));
+            hi = fmaxf(fmaxf(hi, v.x), fmaxf(v.y, fmaxf(v.z, v.w)));
+        }
+    else if (r0 < 3)
         for (int r = r0; r < L::ROWS; r += 3)
         {
             const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
@@ -337,12 +353,9 @@ __device__ __forceinline__ void factor_range(const float* __restrict__ origin, i
                 hi = fmaxf(hi, e[i] < 1e29f ? e[i] : -Limits<float>::inf());
             }
         }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-    {
-        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-    }
+    // Warp minimum and maximum with the integer warp-reduce instruction on an order-preserving image of the floats.
+    lo = from_ordered(__reduce_min_sync(0xffffffffu, to_ordered(lo)));
+    hi = from_ordered(__reduce_max_sync(0xffffffffu, to_ordered(hi)));
 }
 
 /// (E, A) of the warp's block for sign s, scale a2 and centre Mx.
@@ -638,6 +651,13 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     const T fill0 = any_pos ? -Limits<T>::big() : Limits<T>::big();   // slot 0 serves alpha >= 0 unless every alpha is negative
     const uint32_t slot_bytes = static_cast<uint32_t>(a.chunk) * welems * sizeof(T);
     const bool border = window_leaves_image(g, tile_h0, tile_w0);
+    // Factorised path: does the warp's block of the window (32 x 8 pixels plus halo) lie inside the image?
+    [[maybe_unused]] bool block_inside = false;
+    if constexpr (FACTOR)
+    {
+        const int r0 = tile_h0 - g.halo_top() + 8 * (static_cast<int>(threadIdx.x >> 5) >> 1), c0 = tile_w0 - g.halo_left() + 32 * ((threadIdx.x >> 5) & 1);
+        block_inside = r0 >= 0 && r0 + FactorLayout<FACTOR ? KW : 3>::ROWS <= g.H && c0 >= 0 && c0 + FactorLayout<FACTOR ? KW : 3>::WS <= g.W;
+    }
     auto issue = [&](int n) {
         uint64_t* bar = full + (n & 1);
         T* stage = sx0 + (n & 1) * 2 * slot_elems;
@@ -821,7 +841,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                         const float* origin = win + (8 * (warp >> 1)) * FactorLayout<KW>::STRIDE + 32 * (warp & 1);
                         if (!have_range)
                         {
-                            factor_range<KW>(origin, lane, x_lo, x_hi);
+                            factor_range<KW>(origin, lane, x_lo, x_hi, block_inside);
                             have_range = true;
                         }
                         const float2 pr = spair[c * OB + o];   // (Mw, range of w)
