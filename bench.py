@@ -59,7 +59,8 @@ def measure_peaks():
         PEAK_GTAPS["morph_f32"] = max(r["add_max_taps"], r["add_max3_taps"], r["add2_max3_taps"])
         PEAK_GTAPS["morph_f64"] = max(r["f64_add_fmax_taps"], r["f64_add_select_taps"])
         # smorph forward (sum / mean / identity merges): the factorised kernel needs 3 fused multiply-adds per tap and
-        # no exponential; smorph backward: 11 FP32 operations and one ex2 per tap (kernel table).
+        # no exponential; smorph backward: 11 FP32 operations (u, d, scale, sum e, e d, sum e d, sum e d^2, two for c_k,
+        # grad_input and grad_weight accumulation) and one ex2 per tap.
         PEAK_GTAPS["smorph_fwd_f32"] = r["fma_ops"] / 3
         PEAK_GTAPS["smorph_bwd_f32"] = min(r["ex2_ops"], r["fma_ops"] / 11)
         PEAK_GTAPS["smorph_fwdbwd_f32"] = 1.0 / (1.0 / PEAK_GTAPS["smorph_fwd_f32"] + 1.0 / PEAK_GTAPS["smorph_bwd_f32"])
