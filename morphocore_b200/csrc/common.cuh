@@ -107,6 +107,21 @@ __device__ __forceinline__ void thread_patch(int tile_h0, int tile_w0, int H, in
     warp_live = tile_w0 + 32 * (warp & 1) < W && tile_h0 + 8 * (warp >> 1) < H;
 }
 
+/// thread_patch for kernels that can divide their output channels between two warps: when the right half of the
+/// tile lies outside the image (the last tile column of a 224-wide image), both warps of a warp row take the
+/// left 32 x 8 block and `half` (0 or 1) tells which half of the CTA's output channels the warp computes, so that
+/// no warp idles. `split` is false (and the mapping that of thread_patch) when `allow` is false.
+__device__ __forceinline__ void thread_patch_split(int tile_h0, int tile_w0, int H, int W, bool allow, int& tx, int& ty, bool& warp_live, bool& split,
+                                                   int& half)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    split = allow && tile_w0 + 32 >= W;
+    half = split ? (warp & 1) : 0;
+    tx = (lane & 7) + (split ? 0 : 8 * (warp & 1));
+    ty = (lane >> 3) + 4 * (warp >> 1);
+    warp_live = (split || tile_w0 + 32 * (warp & 1) < W) && tile_h0 + 8 * (warp >> 1) < H;
+}
+
 template <typename T> struct Limits;
 template <> struct Limits<float>
 {

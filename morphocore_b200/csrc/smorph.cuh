@@ -614,9 +614,13 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     const int tile = (blockIdx.x / a.o_groups) % tiles;
     const int b = blockIdx.x / (a.o_groups * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    int tx, ty;
-    bool warp_live;
-    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
+    int tx, ty, half;
+    bool warp_live, split;
+    thread_patch_split(tile_h0, tile_w0, g.H, g.W, OB >= 2, tx, ty, warp_live, split, half);
+    // Output channels of this warp: slots 0 .. o_count - 1 of the per-channel register arrays hold channels
+    // o0 + o_base + slot (all OB of them unless the tile is split between the warps of a row, see thread_patch_split).
+    const int o_count = split ? OB / 2 : OB, o_base = half * (OB / 2);
+    const int wx = split ? 0 : static_cast<int>((threadIdx.x >> 5) & 1);   // column block of the warp
     const int o0 = og * OB;
     const int64_t plane = g.plane();
     const T* xb = a.x + static_cast<int64_t>(b) * g.Ci * plane;
@@ -655,7 +659,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
     [[maybe_unused]] bool block_inside = false;
     if constexpr (FACTOR)
     {
-        const int r0 = tile_h0 - g.halo_top() + 8 * (static_cast<int>(threadIdx.x >> 5) >> 1), c0 = tile_w0 - g.halo_left() + 32 * ((threadIdx.x >> 5) & 1);
+        const int r0 = tile_h0 - g.halo_top() + 8 * (static_cast<int>(threadIdx.x >> 5) >> 1), c0 = tile_w0 - g.halo_left() + 32 * wx;
         block_inside = r0 >= 0 && r0 + FactorLayout<FACTOR ? KW : 3>::ROWS <= g.H && c0 >= 0 && c0 + FactorLayout<FACTOR ? KW : 3>::WS <= g.W;
     }
     auto issue = [&](int n) {
@@ -687,8 +691,8 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 if constexpr (STATS)
                 {
                     const int h = tile_h0 + ty * PATCH_H + rr, w = tile_w0 + tx * PATCH_W + j;
-                    target[o][rr][j] = (o0 + o < g.Co && h < g.H && w < g.W)
-                                           ? __ldg(a.target + ((static_cast<int64_t>(b) * g.Co + o0 + o) * g.H + h) * g.W + w) : T(0);
+                    target[o][rr][j] = (o0 + o_base + o < g.Co && h < g.H && w < g.W)
+                                           ? __ldg(a.target + ((static_cast<int64_t>(b) * g.Co + o0 + o_base + o) * g.H + h) * g.W + w) : T(0);
                 }
             }
 
@@ -700,7 +704,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
 #pragma unroll
         for (int o = 0; o < OB; o++)
         {
-            const T bt = o0 + o < g.Co ? __ldg(a.beta + o0 + o) : T(0);
+            const T bt = o0 + o_base + o < g.Co ? __ldg(a.beta + o0 + o_base + o) : T(0);
             soft_sign[o] = bt >= T(0) ? T(1) : T(-1);
             soft_scale[o] = exp_scale(bt >= T(0) ? bt : -bt);
 #pragma unroll
@@ -830,7 +834,9 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
 #pragma unroll
             for (int o = 0; o < OB; o++)
             {
-                const T s = sa[(c * OB + o) * 2], scale = sa[(c * OB + o) * 2 + 1];
+                if (o >= o_count) break;
+                const int os = o_base + o;   // position of the channel in the staged tables
+                const T s = sa[(c * OB + os) * 2], scale = sa[(c * OB + os) * 2 + 1];
                 const T* win = window_of(stage, c, s < T(0));
                 T out[PATCH_H][PATCH_W];
                 if constexpr (FACTOR)
@@ -838,13 +844,13 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                     if (factorise)
                     {
                         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-                        const float* origin = win + (8 * (warp >> 1)) * FactorLayout<KW>::STRIDE + 32 * (warp & 1);
+                        const float* origin = win + (8 * (warp >> 1)) * FactorLayout<KW>::STRIDE + 32 * wx;
                         if (!have_range)
                         {
                             factor_range<KW>(origin, lane, x_lo, x_hi, block_inside);
                             have_range = true;
                         }
-                        const float2 pr = spair[c * OB + o];   // (Mw, range of w)
+                        const float2 pr = spair[c * OB + os];   // (Mw, range of w)
                         if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE)
                         {
                             if (!(held_s == s && held_scale == scale))
@@ -856,7 +862,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                             }
                             float2 acc[PATCH_H][PATCH_W];
                             float rest[PATCH_H][PATCH_W];
-                            factor_pair<KW>(sea, seb + c * taps * OB + o, OB, lane, acc, rest);
+                            factor_pair<KW>(sea, seb + c * taps * OB + os, OB, lane, acc, rest);
                             // out = s (Mx + Mw + N / S); the merge is a sum (a lone pair for identity), so the
                             // constant part is added up per output channel and joins the pixels at the end.
                             offset[o] += s * (held_centre + pr.x);
@@ -875,7 +881,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                     for (int rr = 0; rr < PATCH_H; rr++)
                     {
                         T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
-                        smorph3_values(win, sw + c * taps * OB + o, OB, s, g, tx, ty, rr, d);
+                        smorph3_values(win, sw + c * taps * OB + os, OB, s, g, tx, ty, rr, d);
                         smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
 #pragma unroll
                         for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
@@ -884,7 +890,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                 else
                 {
                     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
-                    smorph_pair<0, KW>(win, sw + c * taps * OB + o, OB, s, scale, g, tx, ty, ref, inv_sum, out);
+                    smorph_pair<0, KW>(win, sw + c * taps * OB + os, OB, s, scale, g, tx, ty, ref, inv_sum, out);
                 }
                 // The merge mode is the same for every pixel: one switch around the pixel loops.
                 auto for_pixels = [&](auto f) {
@@ -931,9 +937,9 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
             for (int j = 0; j < PATCH_W; j++)
             {
                 const int h = tile_h0 + ty * PATCH_H + rr, w = tile_w0 + tx * PATCH_W + j;
-                if (o0 + o >= g.Co || h >= g.H || w >= g.W) continue;
+                if (o >= o_count || !warp_live || o0 + o_base + o >= g.Co || h >= g.H || w >= g.W) continue;
                 T v = merged[o][rr][j];
-                const int64_t at = ((static_cast<int64_t>(b) * g.Co + o0 + o) * g.H + h) * g.W + w;
+                const int64_t at = ((static_cast<int64_t>(b) * g.Co + o0 + o_base + o) * g.H + h) * g.W + w;
                 if constexpr (SOFT)
                 {
                     const T inv = T(1) / soft_s[o][rr][j];
@@ -1127,9 +1133,13 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     const int tile = (blockIdx.x / g.Ci) % tiles;
     const int b = blockIdx.x / (g.Ci * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    int tx, ty;
-    bool warp_live;
-    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
+    // When the right half of the tile is outside the image the two warps of a warp row share the left block and
+    // take every other output channel of the chunk (thread_patch_split): their register windows of grad_input
+    // meet in the shared window, their bins are per warp anyway.
+    int tx, ty, half;
+    bool warp_live, split;
+    thread_patch_split(tile_h0, tile_w0, g.H, g.W, !g.identity, tx, ty, warp_live, split, half);
+    const int o_step = split ? 2 : 1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t plane = g.plane();
     const int wci = g.identity ? 1 : g.Ci;
@@ -1199,11 +1209,11 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
         if (warp_live)
         {
             T grad[PATCH_H][PATCH_W], next[PATCH_H][PATCH_W];
-            load_grad(oc0, grad);
-            for (int oo = 0; oo < oc; oo++)
+            if (half < oc) load_grad(oc0 + half, grad);
+            for (int oo = half; oo < oc; oo += o_step)
             {
                 const int o = oc0 + oo;
-                if (oo + 1 < oc) load_grad(o + 1, next);  // the next channel's gradients arrive while this one computes
+                if (oo + o_step < oc) load_grad(o + o_step, next);  // the next channel's gradients arrive while this one computes
                 const T s = spar[oo * 3], abs_alpha = spar[oo * 3 + 1], scale = spar[oo * 3 + 2];
                 const bool neg = s < T(0);
                 const T* win = sx + (neg ? welems : 0);
