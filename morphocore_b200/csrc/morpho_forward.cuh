@@ -44,7 +44,7 @@ template <int OB, typename T>
 __device__ __forceinline__ void load_weights(T (&dst)[OB], const T* src)
 {
     if constexpr ((OB * sizeof(T)) % 16 == 0)
-    {
+    {   // callers pass a 16-byte aligned source whenever OB values fill whole vectors
         constexpr int PER = 16 / sizeof(T);
 #pragma unroll
         for (int v = 0; v < OB / PER; v++) lds128(&dst[v * PER], src + v * PER);
@@ -56,8 +56,9 @@ __device__ __forceinline__ void load_weights(T (&dst)[OB], const T* src)
     }
 }
 
-/// Extremum over the structuring element of one staged channel, for the thread's OB x 2 x 4 block.
-template <typename T, bool IS_MIN, int KW, int OB, bool PACKED>
+/// Extremum over the structuring element of one staged channel, for the thread's OB x 2 x 4 block. The staged
+/// structuring elements hold WS output channels per tap, of which the OB from `wk` on are used.
+template <typename T, bool IS_MIN, int KW, int OB, bool PACKED, int WS = OB>
 __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], const T* __restrict__ win, const T* __restrict__ wk,
                                                 const Geometry& g, int tx, int ty)
 {
@@ -74,7 +75,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
             T seg[PATCH_H][LEN];
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], base + (rr + KW - 1 - kh) * STRIDE);
-            const T* wrow = wk + kh * KW * OB;
+            const T* wrow = wk + kh * KW * WS;
             if constexpr (sizeof(T) == 4 && PACKED && PACKED_ADD)
             {
                 // Packed adds (add.f32x2): two adjacent pixels per instruction. Pixel pairs start at segment
@@ -94,8 +95,8 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
                 for (int kw = 0; kw + 1 < KW; kw += 2)
                 {
                     T w0[OB], w1[OB];
-                    load_weights<OB>(w0, wrow + kw * OB);
-                    load_weights<OB>(w1, wrow + (kw + 1) * OB);
+                    load_weights<OB>(w0, wrow + kw * WS);
+                    load_weights<OB>(w1, wrow + (kw + 1) * WS);
 #pragma unroll
                     for (int o = 0; o < OB; o++)
                     {
@@ -115,7 +116,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
                 if constexpr (KW & 1)
                 {
                     T w0[OB];
-                    load_weights<OB>(w0, wrow + (KW - 1) * OB);
+                    load_weights<OB>(w0, wrow + (KW - 1) * WS);
 #pragma unroll
                     for (int o = 0; o < OB; o++)
                     {
@@ -138,8 +139,8 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
             for (int kw = 0; kw + 1 < KW; kw += 2)
             {
                 T w0[OB], w1[OB];
-                load_weights<OB>(w0, wrow + kw * OB);
-                load_weights<OB>(w1, wrow + (kw + 1) * OB);
+                load_weights<OB>(w0, wrow + kw * WS);
+                load_weights<OB>(w1, wrow + (kw + 1) * WS);
 #pragma unroll
                 for (int o = 0; o < OB; o++)
 #pragma unroll
@@ -151,7 +152,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
             if constexpr (KW & 1)
             {
                 T w0[OB];
-                load_weights<OB>(w0, wrow + (KW - 1) * OB);
+                load_weights<OB>(w0, wrow + (KW - 1) * WS);
 #pragma unroll
                 for (int o = 0; o < OB; o++)
 #pragma unroll
@@ -171,7 +172,7 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
             for (int kw = 0; kw < g.kW; kw++)
             {
                 T w0[OB];
-                load_weights<OB>(w0, wk + (kh * g.kW + kw) * OB);
+                load_weights<OB>(w0, wk + (kh * g.kW + kw) * WS);
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -223,9 +224,13 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
     const int tile = (blockIdx.x / a.o_groups) % tiles;
     const int b = blockIdx.x / (a.o_groups * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
-    int tx, ty;
-    bool warp_live;
-    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
+    // A tile whose right half is outside the image is split between the warps of each warp row: both take the
+    // left block and half of the output channels (thread_patch_split); slots 0 .. o_count - 1 of the register
+    // arrays then hold channels o0 + o_base + slot.
+    int tx, ty, half;
+    bool warp_live, split;
+    thread_patch_split(tile_h0, tile_w0, g.H, g.W, OB >= 2, tx, ty, warp_live, split, half);
+    const int o_count = split ? OB / 2 : OB, o_base = half * (OB / 2);
     const int o0 = og * OB;
     const int64_t plane = g.plane();
     const T* xb = a.x + static_cast<int64_t>(b) * g.Ci * plane;
@@ -314,18 +319,31 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
 #pragma unroll
                     for (int j = 0; j < PATCH_W; j++) acc[o][rr][j] = op_init;
 
-            window_extremum<T, IS_MIN, KW, OB, !TRACK>(acc,  // the index-tracking variant has no registers to spare for the pair copies
-                                                            sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
+            // (the index-tracking variant has no registers to spare for the pair copies of the packed adds)
+            bool done = false;
+            if constexpr (OB >= 2)
+            {
+                if (split)
+                {
+                    auto& lower = reinterpret_cast<T (&)[OB / 2][PATCH_H][PATCH_W]>(acc);
+                    window_extremum<T, IS_MIN, KW, OB / 2, !TRACK, OB>(lower, sx + c * g.window_elems(), sw + c * g.taps() * OB + o_base, g, tx, ty);
+                    done = true;
+                }
+            }
+            if (!done) window_extremum<T, IS_MIN, KW, OB, !TRACK>(acc, sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
 
             const int ci = c0 + c;
             // The merge mode is the same for every pixel: one switch around the pixel loops.
             auto for_values = [&](auto f) {
 #pragma unroll
                 for (int o = 0; o < OB; o++)
+                {
+                    if (o >= o_count) break;
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
                         for (int j = 0; j < PATCH_W; j++) f(merged[o][rr][j], acc[o][rr][j], winner[TRACK ? o : 0][rr][j]);
+                }
             };
             if (a.merge == MC_MERGE_MAX)
                 for_values([&](T& m, T v, int& win) {
@@ -346,7 +364,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
 #pragma unroll
     for (int o = 0; o < OB; o++)
     {
-        if (o0 + o >= g.Co) continue;
+        if (o >= o_count || !warp_live || o0 + o_base + o >= g.Co) continue;
 #pragma unroll
         for (int rr = 0; rr < PATCH_H; rr++)
         {
@@ -356,7 +374,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
             T out[PATCH_W];
 #pragma unroll
             for (int j = 0; j < PATCH_W; j++) out[j] = a.merge == MC_MERGE_AVERAGE ? merged[o][rr][j] / divisor : merged[o][rr][j];
-            const int64_t row = ((static_cast<int64_t>(b) * g.Co + o0 + o) * g.H + h) * g.W;
+            const int64_t row = ((static_cast<int64_t>(b) * g.Co + o0 + o_base + o) * g.H + h) * g.W;
             if (a.y != nullptr)
             {
                 if (a.vec_store && w0 + PATCH_W <= g.W)
