@@ -185,10 +185,29 @@ def run_cfg5(args, rank, world, device):
         opt.step()
         return loss
 
-    def step_e2e():
-        x = x_host.to(device, non_blocking=True)
-        t = t_host.to(device, non_blocking=True)
-        return step(x, t).item()
+    # End to end: every step's inputs cross PCIe from pinned host memory and its loss is read back. As in any
+    # input pipeline, the copy of step i + 1 runs on a copy stream into the other of two device buffers while
+    # step i computes; the first copy of a run is exposed.
+    copy_stream = torch.cuda.Stream(device=device)
+    staged = [(torch.empty_like(x_dev), torch.empty_like(t_dev)) for _ in range(2)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def prefetch(i):
+        with torch.cuda.stream(copy_stream):
+            staged[i % 2][0].copy_(x_host, non_blocking=True)
+            staged[i % 2][1].copy_(t_host, non_blocking=True)
+            ready[i % 2].record(copy_stream)
+
+    def run_e2e(steps):
+        last = None
+        prefetch(0)
+        for i in range(steps):
+            torch.cuda.current_stream().wait_event(ready[i % 2])
+            loss = step(*staged[i % 2])
+            if i + 1 < steps:
+                prefetch(i + 1)   # the buffer it overwrites was last read by step i - 1, which .item() below has waited for
+            last = loss.item()
+        return last
 
     def barrier():
         if world > 1:
@@ -218,12 +237,11 @@ def run_cfg5(args, rank, world, device):
     launches = _native.launch_count() - launches0
     clocks = sampler.stop()
 
-    step_e2e()
+    run_e2e(1)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        last_loss = step_e2e()
+    last_loss = run_e2e(args.steps)
     e1.record()
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
@@ -232,7 +250,8 @@ def run_cfg5(args, rank, world, device):
     out = {
         "value": n_taps / ms / 1e6, "ms_per_step": ms, "gpu_launches": int(launches), "clocks": clocks,
         "e2e": {"value": n_taps / ms_e2e / 1e6, "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": int(x_host.numel() * 4 + t_host.numel() * 4), "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": int(x_host.numel() * 4 + t_host.numel() * 4), "d2h_bytes_per_step": 4,
+                "pipeline": "copy of step i+1 on a copy stream overlaps step i (two device buffers); first copy exposed"},
         "config": {"workload": "config 5: training step of Dilation(3->64,3x3,sum)->SMorph(64->64,3x3,sum,alpha=2)->Erosion(64->64,5x5,max)->"
                                "SMorph(64->64,3x3,mean,alpha=-2), MSE loss, grad all-reduce, SGD",
                    "global_batch": B, "per_gpu_batch": count, "image": "3x224x224", "n_taps_per_step": n_taps,
