@@ -105,7 +105,10 @@ __device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* 
         ref[rr][j] = ext2<false>(ref[rr][j], fma(s, xv, swk[(kh * kwr + kw) * wstride]));
     });
 
-    T sum[PATCH_H][PATCH_W], weighted[PATCH_H][PATCH_W];
+    // d_k = (s x - ref) + s w_k: for the taps that carry the weight s x is close to ref, so the first difference is exact
+    // and the sum rounds at the size of d_k, not at the size of u_k. A pixel all of whose taps are excluded (far outside
+    // the image, partial tiles) keeps ref above the excluded values, so that its exponentials are 0 rather than 2^(scale w).
+    T sum[PATCH_H][PATCH_W], weighted[PATCH_H][PATCH_W], minus_ref[PATCH_H][PATCH_W];
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -113,20 +116,22 @@ __device__ __forceinline__ void smorph_pair(const T* __restrict__ win, const T* 
         {
             sum[rr][j] = T(0);
             weighted[rr][j] = T(0);
+            ref[rr][j] = ext2<false>(ref[rr][j], -Limits<T>::big() / T(16));
+            minus_ref[rr][j] = -ref[rr][j];
         }
     for_each_tap<KH, KW>(win, g, tx, ty, [&](int kh, int kw, int rr, int j, T xv) {
-        const T u = fma(s, xv, swk[(kh * kwr + kw) * wstride]);
-        const T e = soft_exp(u - ref[rr][j], scale);
+        const T d = fma(s, xv, minus_ref[rr][j]) + swk[(kh * kwr + kw) * wstride];
+        const T e = soft_exp(d, scale);
         sum[rr][j] += e;
-        weighted[rr][j] = fma(e, u, weighted[rr][j]);
+        weighted[rr][j] = fma(e, d, weighted[rr][j]);   // relative to ref: the taps that carry the weight have small d
     });
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
         for (int j = 0; j < PATCH_W; j++)
         {
-            inv_sum[rr][j] = soft_rcp(sum[rr][j]);
-            out[rr][j] = weighted[rr][j] * inv_sum[rr][j];
+            inv_sum[rr][j] = sum[rr][j] > T(0) ? soft_rcp(sum[rr][j]) : T(0);
+            out[rr][j] = fma(weighted[rr][j], inv_sum[rr][j], ref[rr][j]);
         }
 }
 
@@ -390,9 +395,12 @@ __device__ __forceinline__ void factor_fill(const float* __restrict__ origin, fl
 /// S and N of one pair for the thread's patch: acc = (S, sum A Ew), rest = sum E Bw, N = acc.y + rest.
 /// `eb` holds (Ew_k, Bw_k) of the pair, element k at eb[k * wstride]. Every row of the (E, A) block is loaded
 /// once and serves the kernel rows of both patch rows that read it.
-template <int KW>
+/// `shift` (backward pass) moves the centre of the linear factor for this thread: A' = A - shift E = E (s x - Mx - shift),
+/// so that N becomes sum_k e_k (d_k - shift). With shift near the soft extremum of the thread's pixels the sum is small
+/// and its rounding error, which the backward pass multiplies by |alpha|, shrinks with it.
+template <int KW, bool RECENTRE = false>
 __device__ __forceinline__ void factor_pair(const float4* __restrict__ ea, const float2* __restrict__ eb, int wstride, int lane,
-                                            float2 (&acc)[PATCH_H][PATCH_W], float (&rest)[PATCH_H][PATCH_W])
+                                            float2 (&acc)[PATCH_H][PATCH_W], float (&rest)[PATCH_H][PATCH_W], float shift = 0.0f)
 {
     using L = FactorLayout<KW>;
     static_assert(PATCH_H == 2, "the row schedule below is written for two patch rows");
@@ -414,8 +422,8 @@ __device__ __forceinline__ void factor_pair(const float4* __restrict__ ea, const
         for (int v = 0; v < L::LEN / 2; v++)
         {
             const float4 t = src[v];
-            seg[2 * v] = make_float2(t.x, t.y);
-            seg[2 * v + 1] = make_float2(t.z, t.w);
+            seg[2 * v] = make_float2(t.x, RECENTRE ? fmaf(-shift, t.x, t.y) : t.y);
+            seg[2 * v + 1] = make_float2(t.z, RECENTRE ? fmaf(-shift, t.z, t.w) : t.w);
         }
         auto apply = [&](int rr, int kh) {
 #pragma unroll
@@ -1048,6 +1056,7 @@ struct SmorphBackwardArgs
     T* gbeta;           // smooth merge: gradient of beta
     int o_chunk;      // output channels whose weights and bins are staged together
     T scale;          // 1 / Ci for AVERAGE
+    int factorise;    // 5 x 5 and 7 x 7 float kernels: S and N of a pair from the factorised sums where that is safe
 };
 
 /// Backward of one pair for the thread's patch. Recomputes the forward state (ref, S, out), then every tap
@@ -1070,11 +1079,16 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
     T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W], out[PATCH_H][PATCH_W];
     smorph_pair<0, KW>(win, swk, 1, s, scale, g, tx, ty, ref, inv_sum, out);  // kernel rows not unrolled: smaller code, fewer live registers
 
-    T scaled[PATCH_H][PATCH_W];
+    T scaled[PATCH_H][PATCH_W], minus_ref[PATCH_H][PATCH_W], out_d[PATCH_H][PATCH_W];
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-        for (int j = 0; j < PATCH_W; j++) scaled[rr][j] = grad[rr][j] * inv_sum[rr][j];
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            scaled[rr][j] = grad[rr][j] * inv_sum[rr][j];
+            minus_ref[rr][j] = -ref[rr][j];
+            out_d[rr][j] = out[rr][j] - ref[rr][j];
+        }
 
     T alpha_sum = T(0), tap_sum = T(0);
     int current = -1;
@@ -1090,10 +1104,9 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
             if (current >= 0) flush_tap(current);
             current = k;
         }
-        const T u = fma(s, xv, swk[k]);
-        const T d = u - ref[rr][j];
+        const T d = fma(s, xv, minus_ref[rr][j]) + swk[k];   // as in smorph_pair
         const T pg = soft_exp(d, scale) * scaled[rr][j];
-        const T centered = u - out[rr][j];
+        const T centered = d - out_d[rr][j];
         const T c = fma(abs_alpha * pg, centered, pg);
         if constexpr (KH > 0) gxr[rr + KH - 1 - kh][j + KW - 1 - kw] += c;
         else if (c != T(0)) atomic_add(sg + (ty * PATCH_H + rr + g.kH - 1 - kh) * g.win_stride + tx * PATCH_W + g.seg_off + j + g.kW - 1 - kw, c);
@@ -1101,6 +1114,136 @@ __device__ __forceinline__ void smorph_pair_backward(const T* __restrict__ win, 
         alpha_sum = fma(pg * d, centered, alpha_sum);
     });
     flush_tap(current);
+    alpha_sum = warp_sum(alpha_sum);
+    if (lane == 0) *abin = alpha_sum;
+}
+
+/// float kernels with square 5 x 5 and 7 x 7 structuring elements split the backward of a pair into per-pixel
+/// statistics (the soft extremum out_u and the sum of the exponentials) and one gradient pass over the taps
+/// (smorph_taps_backward); the statistics come from the factorised sums where that is safe (backward_factorises,
+/// smorph_stats_factored) and from the max-subtracting passes otherwise (smorph_stats_stable).
+template <typename T, int KH, int KW>
+__host__ __device__ constexpr bool backward_splits() { return sizeof(T) == 4 && KH == KW && KW >= 5 && KW <= 7; }
+template <typename T, int KH, int KW, bool SOFT>
+__host__ __device__ constexpr bool backward_factorises() { return backward_splits<T, KH, KW>() && !SOFT; }
+
+/// Statistics of one pair from the factorised form (see "Factorised forward"): `ea` holds (E, A) of the warp's block for
+/// this pair's sign and scale, `eb` the pair's (Ew, Bw), and `ref` = Mx + Mw bounds every u_k from above. factor_pair
+/// gives S = sum_k 2^(scale (u_k - ref)) and N = sum_k 2^(scale (u_k - ref)) (u_k - ref) in three fused multiply-adds
+/// per tap, no maximum and no exponential (N is summed relative to `shift`, see factor_pair). Out: centre = out_u = ref + N / S and scaled = g / S' with
+/// S' = sum_k 2^(scale (u_k - out_u)) = S 2^(-scale N / S), the sum the gradient pass works with.
+template <int KW>
+__device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__ ea, const float2* __restrict__ eb, int lane, float scale, float ref,
+                                                      float shift, const float (&grad)[PATCH_H][PATCH_W], float (&centre)[PATCH_H][PATCH_W],
+                                                      float (&scaled)[PATCH_H][PATCH_W])
+{
+    float2 acc[PATCH_H][PATCH_W];
+    float rest[PATCH_H][PATCH_W];
+    factor_pair<KW, true>(ea, eb, 1, lane, acc, rest, shift);
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            // A pixel far outside the image (partial tiles) has no tap at all: S = 0, and it carries no gradient.
+            const float inv_sum = acc[rr][j].x > 0.0f ? soft_rcp(acc[rr][j].x) : 0.0f;
+            const float out_d = acc[rr][j].x > 0.0f ? fmaf(acc[rr][j].y + rest[rr][j], inv_sum, shift) : 0.0f;   // <= 0
+            centre[rr][j] = ref + out_d;
+            scaled[rr][j] = grad[rr][j] * inv_sum * ex2_approx(fminf(scale * out_d, 0.0f));
+        }
+}
+
+/// The same statistics from the max-subtracting passes (any alpha, any range of the inputs).
+template <int KW>
+__device__ __forceinline__ void smorph_stats_stable(const float* __restrict__ win, const float* __restrict__ swk, float s, float scale,
+                                                    const Geometry& g, int tx, int ty, const float (&grad)[PATCH_H][PATCH_W],
+                                                    float (&centre)[PATCH_H][PATCH_W], float (&scaled)[PATCH_H][PATCH_W])
+{
+    float ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
+    smorph_pair<0, KW>(win, swk, 1, s, scale, g, tx, ty, ref, inv_sum, centre);
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++)
+            // out_u <= ref; the clamp only matters for pixels far outside the image, whose ref and out_u are both -1e30
+            // up to rounding and whose gradient is zero.
+            scaled[rr][j] = grad[rr][j] * inv_sum[rr][j] * ex2_approx(fminf(scale * (centre[rr][j] - ref[rr][j]), 0.0f));
+}
+
+/// Gradient pass of one pair for the thread's patch, exponentials taken relative to the soft extremum itself:
+///     t_k = u_k - out_u = s x + (s w_k - out_u),   e_k = 2^(scale t_k),   G = g / sum_k e_k  (`scaled`),
+///     c_k = e_k (G + |alpha| G t_k)                      to grad_input (register window) and grad_weight,
+///     d out / d alpha = (1 / sum_k e_k) sum_k e_k t_k^2  (the e-weighted mean of t_k is zero).
+/// |alpha| (max_k u_k - out_u) is at most about ln(taps), so e_k stays below 2^5, and the taps that carry the weight
+/// have small t_k, formed by one fused multiply-add: their exponentials are as exact as with the maximum subtracted.
+/// One exponential and ten instructions per tap. The KW tap sums of a kernel row are added over the warp through its
+/// scratch `red` (see smorph3_pair_backward).
+template <int KW>
+__device__ __forceinline__ void smorph_taps_backward(const float* __restrict__ win, const float* __restrict__ swk, float* __restrict__ wbin,
+                                                     float* __restrict__ abin, float* __restrict__ red, float s, float abs_alpha, float scale,
+                                                     const float (&centre)[PATCH_H][PATCH_W], const float (&scaled)[PATCH_H][PATCH_W], int tx, int ty,
+                                                     int lane, float (&gxr)[PATCH_H + KW - 1][PATCH_W + KW - 1])
+{
+    constexpr int LEN = segment_len(KW, 4), OFF = segment_offset(KW, 4), STRIDE = window_stride(KW, 4);
+    static_assert(KW <= RED_ROWS, "one scratch row per tap of a kernel row");
+    float steep[PATCH_H][PATCH_W], spread[PATCH_H][PATCH_W], minus_centre[PATCH_H][PATCH_W];
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            steep[rr][j] = abs_alpha * scaled[rr][j];
+            spread[rr][j] = 0.0f;
+            minus_centre[rr][j] = -centre[rr][j];
+        }
+#pragma unroll
+    for (int kh = 0; kh < KW; kh++)
+    {
+        float seg[PATCH_H][LEN];
+#pragma unroll
+        for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], win + (ty * PATCH_H + rr + KW - 1 - kh) * STRIDE + tx * PATCH_W);
+        float tap_sum[KW];
+#pragma unroll
+        for (int kw = 0; kw < KW; kw++)
+        {
+            const float wv = swk[kh * KW + kw];
+            float sum = 0.0f;
+#pragma unroll
+            for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                for (int j = 0; j < PATCH_W; j++)
+                {
+                    const float t = fmaf(s, seg[rr][OFF + j + KW - 1 - kw], minus_centre[rr][j]) + wv;   // as in smorph_pair
+                    const float e = soft_exp(t, scale);   // exactly 0 for an excluded tap (t = -1e30)
+                    const float et = e * t;               // e first: an excluded tap gives 0 * -1e30 = -0, never an overflow
+                    const float c = fmaf(steep[rr][j], et, e * scaled[rr][j]);
+                    gxr[rr + KW - 1 - kh][j + KW - 1 - kw] += c;
+                    sum += c;
+                    spread[rr][j] = fmaf(et, t, spread[rr][j]);
+                }
+            tap_sum[kw] = sum;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int kw = 0; kw < KW; kw++) red[kw * RED_STRIDE + lane] = tap_sum[kw];
+        __syncwarp();
+        float part = 0.0f;
+        if (lane < 3 * KW)
+        {
+            const float* strip = red + (lane / 3) * RED_STRIDE + (lane % 3) * 11;
+            const int n = (lane % 3) == 2 ? 10 : 11;
+#pragma unroll
+            for (int c = 0; c < 11; c++)
+                if (c < n) part += strip[c];
+        }
+        part += __shfl_down_sync(0xffffffffu, part, 1) + __shfl_down_sync(0xffffffffu, part, 2);
+        if (lane < 3 * KW && lane % 3 == 0) wbin[kh * KW + lane / 3] = part;
+    }
+    float alpha_sum = 0.0f;
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++) alpha_sum = fmaf(spread[rr][j], scaled[rr][j], alpha_sum);
     alpha_sum = warp_sum(alpha_sum);
     if (lane == 0) *abin = alpha_sum;
 }
@@ -1127,6 +1270,14 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     T* abins = wbins + WARPS * OC * taps;      // [WARPS][OC]
     T* bbins = abins + WARPS * OC;             // [WARPS][OC]: gradient of beta (smooth merge)
     T* red = bbins + WARPS * OC + (threadIdx.x >> 5) * RED_ROWS * RED_STRIDE;  // this warp's reduction scratch
+    // Factorised recomputation of S and N (backward_factorises): [OC][taps] (Ew, Bw), [OC] (Mw, range of w), one (E, A) buffer per warp.
+    constexpr bool FACTOR = backward_factorises<T, KH, KW, SOFT>();
+    constexpr int FKW = backward_splits<T, KH, KW>() ? KW : 3;
+    float2* seb = reinterpret_cast<float2*>(smem_raw + (reinterpret_cast<unsigned char*>(bbins + WARPS * OC + WARPS * RED_ROWS * RED_STRIDE) - smem_raw + 15) / 16 * 16);
+    float2* spair = seb + OC * taps;
+    float4* sea = reinterpret_cast<float4*>(smem_raw + (reinterpret_cast<unsigned char*>(spair + OC) - smem_raw + 15) / 16 * 16)
+                  + (threadIdx.x >> 5) * (FactorLayout<FKW>::BYTES / 16);
+    const bool factorise = FACTOR && a.factorise != 0;
 
     const int tiles = g.tiles_x * g.tiles_y;
     const int ci = blockIdx.x % g.Ci;
@@ -1184,6 +1335,13 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
 #pragma unroll
         for (int c = 0; c < GW; c++) gxr[r][c] = T(0);
 
+    // Factorised path: the warp's block of the window (32 x 8 pixels plus halo), the range of x in it (taken once, after
+    // the first barrier below) and what the warp's (E, A) buffer holds.
+    [[maybe_unused]] const int block_at = 8 * (warp >> 1) * g.win_stride + 32 * (split ? 0 : (warp & 1));
+    [[maybe_unused]] float x_lo = 0.0f, x_hi = 0.0f, held_s = 0.0f, held_scale = -1.0f, held_centre = 0.0f;
+    [[maybe_unused]] bool have_range = false;
+    [[maybe_unused]] float local_lo = Limits<float>::inf(), local_hi = -Limits<float>::inf();
+
     for (int oc0 = o_begin; oc0 < o_end; oc0 += OC)
     {
         const int oc = min(OC, o_end - oc0);
@@ -1204,10 +1362,66 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             sw[e] = al >= T(0) ? v : -v;
         }
         for (int e = threadIdx.x; e < WARPS * OC * (taps + 2); e += THREADS) wbins[e] = T(0);  // bins of warps that skip stay zero
+        if constexpr (FACTOR)
+        {
+            if (factorise)
+            {
+                // One warp per pair, one lane per tap (two for 7 x 7): Mw and the range of s w by shuffles, then (Ew, Bw).
+                for (int oo = warp; oo < oc; oo += WARPS)
+                {
+                    const float al = __ldg(a.alpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci));
+                    const float sgn = al >= 0.0f ? 1.0f : -1.0f, scale = exp_scale(fabsf(al));
+                    const float* wp = a.w + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps;
+                    float lo = Limits<float>::inf(), hi = -Limits<float>::inf();
+                    for (int k = lane; k < taps; k += 32)
+                    {
+                        const float v = sgn * __ldg(wp + k);
+                        lo = fminf(lo, v);
+                        hi = fmaxf(hi, v);
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1)
+                    {
+                        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+                        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+                    }
+                    if (lane == 0) spair[oo] = make_float2(hi, hi - lo);
+                    for (int k = lane; k < taps; k += 32)
+                    {
+                        const float d = sgn * __ldg(wp + k) - hi;
+                        const float ew = soft_exp(d, scale);
+                        seb[oo * taps + k] = make_float2(ew, ew * d);
+                    }
+                }
+            }
+        }
         __syncthreads();
 
         if (warp_live)
         {
+            if constexpr (FACTOR)
+            {
+                if (factorise && !have_range)
+                {
+                    const int r0 = tile_h0 - g.halo_top() + 8 * (warp >> 1), c0 = tile_w0 - g.halo_left() + 32 * (split ? 0 : (warp & 1));
+                    const bool inside = r0 >= 0 && r0 + FactorLayout<FKW>::ROWS <= g.H && c0 >= 0 && c0 + FactorLayout<FKW>::WS <= g.W;
+                    factor_range<FKW>((has_pos ? sx : sx + welems) + block_at, lane, x_lo, x_hi, inside);
+                    have_range = true;
+                    // Largest and smallest x the thread's own pixels can read: the centre of its linear sums (factor_pair).
+                    constexpr int LEN = segment_len(FKW, 4), OFF = segment_offset(FKW, 4);
+                    for (int r = 0; r < PATCH_H + FKW - 1; r++)
+                    {
+                        float seg[LEN];
+                        load_segment<LEN>(seg, (has_pos ? sx : sx + welems) + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W);
+#pragma unroll
+                        for (int c = OFF; c < OFF + PATCH_W + FKW - 1; c++)
+                        {
+                            local_lo = fminf(local_lo, seg[c] > -1e29f ? seg[c] : Limits<float>::inf());
+                            local_hi = fmaxf(local_hi, seg[c] < 1e29f ? seg[c] : -Limits<float>::inf());
+                        }
+                    }
+                }
+            }
             T grad[PATCH_H][PATCH_W], next[PATCH_H][PATCH_W];
             if (half < oc) load_grad(oc0 + half, grad);
             for (int oo = half; oo < oc; oo += o_step)
@@ -1293,7 +1507,34 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                     beta_sum = warp_sum(beta_sum);
                     if (lane == 0) bbins[warp * OC + oo] = beta_sum;
                 }
-                if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                if constexpr (backward_splits<T, KH, KW>())
+                {
+                    float centre[PATCH_H][PATCH_W], scaled[PATCH_H][PATCH_W];
+                    bool have_stats = false;
+                    if constexpr (FACTOR)
+                    {
+                        if (factorise)
+                        {
+                            const float2 pr = spair[oo];   // (Mw, range of w)
+                            if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE)
+                            {
+                                if (!(held_s == s && held_scale == scale))
+                                {
+                                    held_centre = s > 0.0f ? x_hi : -x_lo;
+                                    factor_fill<FKW>(win + block_at, sea, s, scale, held_centre, lane);
+                                    held_s = s;
+                                    held_scale = scale;
+                                }
+                                const float shift = local_hi >= local_lo ? (s > 0.0f ? local_hi : -local_lo) - held_centre : 0.0f;
+                                smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, held_centre + pr.x, shift, grad, centre, scaled);
+                                have_stats = true;
+                            }
+                        }
+                    }
+                    if (!have_stats) smorph_stats_stable<FKW>(win, sw + oo * taps, s, scale, g, tx, ty, grad, centre, scaled);
+                    smorph_taps_backward<FKW>(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, centre, scaled, tx, ty, lane, gxr);
+                }
+                else if constexpr (KH == 3 && KW == 3) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
                 else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
 #pragma unroll
                 for (int rr = 0; rr < PATCH_H; rr++)
@@ -1367,15 +1608,24 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     a.beta = beta; a.soft_ref = soft_ref; a.soft_inv = soft_inv; a.gbeta = gbeta;
     a.scale = d.merge == MC_MERGE_AVERAGE ? T(1.0) / static_cast<T>(d.Ci) : T(1.0);
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
-    const size_t fixed = (3 * static_cast<size_t>(a.g.window_elems()) + WARPS * RED_ROWS * RED_STRIDE) * sizeof(T);
-    const size_t per_o = (taps + 3 + WARPS * (taps + 2)) * sizeof(T);
+    // The factorised recomputation of S and N suits the merges without a winner test (see launch_smorph_forward).
+    constexpr bool FACTOR = backward_factorises<T, KH, KW, false>();
+    a.factorise = FACTOR && (d.merge == MC_MERGE_ADD || d.merge == MC_MERGE_AVERAGE || d.merge == MC_MERGE_IDENTITY);
+    size_t fixed = (3 * static_cast<size_t>(a.g.window_elems()) + WARPS * RED_ROWS * RED_STRIDE) * sizeof(T);
+    size_t per_o = (taps + 3 + WARPS * (taps + 2)) * sizeof(T);
+    if (a.factorise)
+    {
+        fixed += 32 + WARPS * static_cast<size_t>(FactorLayout<FACTOR ? KW : 3>::BYTES);
+        per_o += (taps + 1) * sizeof(float2);
+    }
     if (fixed + per_o > MAX_SHARED_BYTES)
     {
         set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
         return MC_ERR_UNSUPPORTED;
     }
     // Chunk of output channels: as many as fit in about 100 KiB (two CTAs per SM).
-    const size_t budget = fixed + per_o > 100 * 1024 ? MAX_SHARED_BYTES : 100 * 1024;
+    // (The 5 x 5 and 7 x 7 float kernels run one CTA per SM anyway: their chunk may take twice that.)
+    const size_t budget = fixed + per_o > 100 * 1024 ? MAX_SHARED_BYTES : (a.factorise ? 200 * 1024 : 100 * 1024);
     int chunk = static_cast<int>((budget - fixed) / per_o);
     chunk = std::max(1, std::min(chunk, a.g.identity ? 1 : d.Co));
     a.o_chunk = chunk;

@@ -218,7 +218,11 @@ def test_smorph_against_oracle(C, k, dtype):
             y = C.smorph_forward(dev(x), dev(w), dev(alpha), merge)
             np.testing.assert_allclose(y.cpu().numpy(), want, **ytol, err_msg=str((merge, k, a0)))
             g = mask_ambiguous_winners(gy, x, w, alpha, merge)
-            wgx, wgw, wga = O.smorph_backward(x, w, alpha, g, merge)
+            # Gradients are checked against the oracle run in double on the same (float) inputs: its float run is
+            # itself up to one full tolerance away from the double one at |alpha| = 8 (measured: 7e-5 on grad_input of
+            # the max merge, 7 x 7), so a float-to-float comparison would test the oracle's rounding, not the kernel's.
+            f64 = np.float64
+            wgx, wgw, wga = O.smorph_backward(x.astype(f64), w.astype(f64), alpha.astype(f64), g.astype(f64), merge)
             gx, gw, ga = C.smorph_backward(dev(x), dev(w), dev(alpha), y, dev(g), merge)
             np.testing.assert_allclose(gx.cpu().numpy(), wgx, **gtol, err_msg=str((merge, k, a0)))
             sums = dict(rtol=gtol["rtol"], atol=gtol["atol"] * 100)
@@ -268,6 +272,47 @@ def test_smorph_factorised_forward_matches_double(C, case, merge):
     # channels a sum adds up
     scale = ci if merge == "sum" else 1
     torch.testing.assert_close(y.double(), ref, rtol=1e-4, atol=1e-5 * scale * max(1.0, spread))
+
+
+@pytest.mark.parametrize("case", [
+    # kernel, image, alphas, spread of x
+    (5, 128, "uniform", 1.0), (5, 97, "per_pair", 1.0), (5, 61, "extreme", 1.0), (7, 128, "uniform_negative", 1.0),
+    (7, 131, "per_pair", 1.0), (7, 70, "extreme", 3.0), (7, 100, "per_pair", 30.0)])
+@pytest.mark.parametrize("merge", ["sum", "mean", "identity"])
+def test_smorph_factorised_backward_matches_double(C, case, merge):
+    """The float backward pass of 5 x 5 and 7 x 7 structuring elements (sum / mean / identity merges) recomputes the
+    sums S and N of a pair from the factorised form wherever the forward pass may use it, and subtracts the maximum
+    elsewhere. Both must agree with the double kernel, which always subtracts the maximum: interior and border
+    blocks, partial tiles, alpha = 0, signs mixed within one input channel, ranges on both sides of the switch."""
+    k, hw, kind, spread = case
+    g = torch.Generator().manual_seed(4321 + k + hw)
+    co, ci = (6, 6) if merge == "identity" else (6, 5)
+    x = (spread * torch.randn((2, ci, hw, hw + 3), generator=g)).cuda()
+    w = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, k, k), generator=g)).cuda()
+    gy = torch.randn((2, co, hw, hw + 3), generator=g).cuda()
+    pairs = (co,) if merge == "identity" else (co, ci)
+    if kind == "uniform":
+        a = torch.full(pairs, 2.0)
+    elif kind == "uniform_negative":
+        a = torch.full(pairs, -8.0)
+    elif kind == "per_pair":
+        a = 3.0 * torch.randn(pairs, generator=g)
+    else:
+        values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, 1e-4, 3.0, 25.0, 400.0])
+        a = values[torch.randint(0, len(values), pairs, generator=g)]
+    a = a.cuda()
+    y = C.smorph_forward(x, w, a, merge)
+    gx, gw, ga = C.smorph_backward(x, w, a, y, gy, merge)
+    yd = C.smorph_forward(x.double(), w.double(), a.double(), merge)
+    rx, rw, ra = C.smorph_backward(x.double(), w.double(), a.double(), yd, gy.double(), merge)
+    for t in (gx, gw, ga):
+        assert torch.isfinite(t).all()
+    # Rounding of exp() is multiplied by |alpha| in the gradients (see smorph_tols); sums over the image are compared
+    # relative to their largest element.
+    amp = max(1.0, float(a.abs().max()) / 10.0)
+    torch.testing.assert_close(gx.double(), rx, rtol=1e-4 * amp, atol=3e-5 * amp * max(1.0, spread))
+    torch.testing.assert_close(gw.double(), rw, rtol=1e-4 * amp, atol=1e-4 * amp * float(rw.abs().max()))
+    torch.testing.assert_close(ga.double(), ra, rtol=1e-4 * amp, atol=1e-4 * amp * float(ra.abs().max()))
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
