@@ -299,7 +299,14 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
 #define MC_PACKED_FMA 1
 #endif
 
-constexpr float FACTOR_RANGE = 80.0f;
+// 2^-96 leaves 30 binades above the smallest normal float for the products with (s x - Mx) and (s w - Mw); the
+// reciprocal of the smallest possible S, 2^96, is far from overflow.
+constexpr float FACTOR_RANGE = 96.0f;
+// The backward pass multiplies the relative error of the exponentials by |alpha| times the gradient, and s x - Mx rounds
+// at the size of the range: it switches to the max-subtracting statistics earlier.
+constexpr float FACTOR_RANGE_BACKWARD = 80.0f;
+// Exponents beyond this many binades are formed with exp2_product (factor_fill).
+constexpr float FACTOR_PRECISE = 32.0f;
 
 template <int KW>
 struct FactorLayout
@@ -327,6 +334,19 @@ __device__ __forceinline__ int to_ordered(float v)
     return i ^ ((i >> 31) & 0x7fffffff);
 }
 __device__ __forceinline__ float from_ordered(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
+
+/// 2^(d * scale) with the product formed exactly: d * scale = hi + lo, hi the nearest integer, lo the remainder taken by
+/// one fused multiply-add, so the result does not inherit the rounding of a product of magnitude up to FACTOR_RANGE
+/// (half an ulp of 100 is a relative error of 2.6e-6 in the exponential, which the backward pass multiplies by |alpha|).
+/// Excluded window elements (d = -1e30) give 0.
+__device__ __forceinline__ float exp2_product(float d, float scale)
+{
+    const float hi = rintf(fmaxf(d * scale, -160.0f));
+    float e_hi, e_lo;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e_hi) : "f"(hi));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e_lo) : "f"(fmaf(d, scale, -hi)));
+    return e_hi * e_lo;
+}
 
 /// Smallest and largest in-image x of the warp's block (window elements outside the image hold +-1e30 and are
 /// masked out; a block that lies inside the image, `inside`, has none and skips the masks).
@@ -364,8 +384,11 @@ __device__ __forceinline__ void factor_range(const float* __restrict__ origin, i
 }
 
 /// (E, A) of the warp's block for sign s, scale a2 and centre Mx.
-template <int KW>
-__device__ __forceinline__ void factor_fill(const float* __restrict__ origin, float4* __restrict__ ea, float s, float scale, float centre, int lane)
+/// `precise` (warp uniform; backward pass only, ALLOW_PRECISE) forms the exponentials with exp2_product: worth its few
+/// extra instructions once the exponents are large.
+template <int KW, bool ALLOW_PRECISE = false>
+__device__ __forceinline__ void factor_fill(const float* __restrict__ origin, float4* __restrict__ ea, float s, float scale, float centre, int lane,
+                                            bool precise = false)
 {
     using L = FactorLayout<KW>;
     __syncwarp();   // every lane is done with the previous contents
@@ -375,7 +398,15 @@ __device__ __forceinline__ void factor_fill(const float* __restrict__ origin, fl
         {
             const float4 v = *reinterpret_cast<const float4*>(origin + r * L::STRIDE + 4 * c);
             const float x0 = fmaf(s, v.x, -centre), x1 = fmaf(s, v.y, -centre), x2 = fmaf(s, v.z, -centre), x3 = fmaf(s, v.w, -centre);
-            const float e0 = soft_exp(x0, scale), e1 = soft_exp(x1, scale), e2 = soft_exp(x2, scale), e3 = soft_exp(x3, scale);
+            float e0, e1, e2, e3;
+            if (ALLOW_PRECISE && precise)
+            {
+                e0 = exp2_product(x0, scale); e1 = exp2_product(x1, scale); e2 = exp2_product(x2, scale); e3 = exp2_product(x3, scale);
+            }
+            else
+            {
+                e0 = soft_exp(x0, scale); e1 = soft_exp(x1, scale); e2 = soft_exp(x2, scale); e3 = soft_exp(x3, scale);
+            }
             const float4 first = make_float4(e0, e0 * x0, e1, e1 * x1), second = make_float4(e2, e2 * x2, e3, e3 * x3);
             float4* row = ea + r * L::ROW_CHUNKS;
             if (2 * c < L::HALF)   // HALF is even: both chunks of the vector fall on the same side
@@ -811,7 +842,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
                     for (int k = lane; k < taps; k += 32)
                     {
                         const float d = sgn * __ldg(wp + k) - hi;
-                        const float ew = soft_exp(d, scale);
+                        const float ew = exp2_product(d, scale);
                         seb[(c * taps + k) * OB + o] = make_float2(ew, ew * d);
                     }
                 }
@@ -1128,12 +1159,12 @@ template <typename T, int KH, int KW, bool SOFT>
 __host__ __device__ constexpr bool backward_factorises() { return backward_splits<T, KH, KW>() && !SOFT; }
 
 /// Statistics of one pair from the factorised form (see "Factorised forward"): `ea` holds (E, A) of the warp's block for
-/// this pair's sign and scale, `eb` the pair's (Ew, Bw), and `ref` = Mx + Mw bounds every u_k from above. factor_pair
+/// this pair's sign and scale, `eb` the pair's (Ew, Bw), and ref = Mx + Mw bounds every u_k from above. factor_pair
 /// gives S = sum_k 2^(scale (u_k - ref)) and N = sum_k 2^(scale (u_k - ref)) (u_k - ref) in three fused multiply-adds
 /// per tap, no maximum and no exponential (N is summed relative to `shift`, see factor_pair). Out: centre = out_u = ref + N / S and scaled = g / S' with
 /// S' = sum_k 2^(scale (u_k - out_u)) = S 2^(-scale N / S), the sum the gradient pass works with.
 template <int KW>
-__device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__ ea, const float2* __restrict__ eb, int lane, float scale, float ref,
+__device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__ ea, const float2* __restrict__ eb, int lane, float scale, float base,
                                                       float shift, const float (&grad)[PATCH_H][PATCH_W], float (&centre)[PATCH_H][PATCH_W],
                                                       float (&scaled)[PATCH_H][PATCH_W])
 {
@@ -1147,9 +1178,12 @@ __device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__
         {
             // A pixel far outside the image (partial tiles) has no tap at all: S = 0, and it carries no gradient.
             const float inv_sum = acc[rr][j].x > 0.0f ? soft_rcp(acc[rr][j].x) : 0.0f;
-            const float out_d = acc[rr][j].x > 0.0f ? fmaf(acc[rr][j].y + rest[rr][j], inv_sum, shift) : 0.0f;   // <= 0
-            centre[rr][j] = ref + out_d;
-            scaled[rr][j] = grad[rr][j] * inv_sum * ex2_approx(fminf(scale * out_d, 0.0f));
+            // out_u = ref + shift + N / S, with `base` = ref + shift formed by the caller without the detour through ref: the
+            // quotient is small, so out_u rounds at its own size. out_u - ref (for S') may round at the size of the range.
+            const float quotient = (acc[rr][j].y + rest[rr][j]) * inv_sum;
+            const float out_d = acc[rr][j].x > 0.0f ? quotient + shift : 0.0f;   // <= 0
+            centre[rr][j] = base + quotient;
+            scaled[rr][j] = grad[rr][j] * (inv_sum * ex2_approx(fminf(scale * out_d, 0.0f)));   // 1 / S' <= 1 first: no overflow
         }
 }
 
@@ -1389,7 +1423,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                     for (int k = lane; k < taps; k += 32)
                     {
                         const float d = sgn * __ldg(wp + k) - hi;
-                        const float ew = soft_exp(d, scale);
+                        const float ew = exp2_product(d, scale);
                         seb[oo * taps + k] = make_float2(ew, ew * d);
                     }
                 }
@@ -1516,17 +1550,18 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                         if (factorise)
                         {
                             const float2 pr = spair[oo];   // (Mw, range of w)
-                            if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE)
+                            if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE_BACKWARD)
                             {
                                 if (!(held_s == s && held_scale == scale))
                                 {
                                     held_centre = s > 0.0f ? x_hi : -x_lo;
-                                    factor_fill<FKW>(win + block_at, sea, s, scale, held_centre, lane);
+                                    factor_fill<FKW, true>(win + block_at, sea, s, scale, held_centre, lane, scale * (x_hi - x_lo) > FACTOR_PRECISE);
                                     held_s = s;
                                     held_scale = scale;
                                 }
-                                const float shift = local_hi >= local_lo ? (s > 0.0f ? local_hi : -local_lo) - held_centre : 0.0f;
-                                smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, held_centre + pr.x, shift, grad, centre, scaled);
+                                // The thread's own largest s x: centre of its linear sums, and with Mw the base of its soft extrema.
+                                const float local = local_hi >= local_lo ? (s > 0.0f ? local_hi : -local_lo) : held_centre;
+                                smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, local + pr.x, local - held_centre, grad, centre, scaled);
                                 have_stats = true;
                             }
                         }
