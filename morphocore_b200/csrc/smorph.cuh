@@ -595,26 +595,26 @@ __device__ __forceinline__ void smorph3_pair_backward(const float* __restrict__ 
     }
 }
 
-/// smorph3_pair_backward (float) without the maximum: `bound` = (the largest s x the thread's pixels can read) + (the
-/// largest s w_k) is at least every u_k of the patch, and the caller has checked that scale * (range of x in the warp's
-/// block + range of w) is small, so that 2^(scale (u_k - bound)) of the taps that carry the weight is far from
-/// underflow. With d_k = u_k - bound formed by the fused multiply-add itself (the tap's constant is s w_k - bound),
-/// the maximum and the subtraction go: about 10 instead of 12.6 FP32 operations per tap. The sums S, sum e d and
-/// sum e d^2 are relative to `bound` instead of the pixel's own maximum; everything after them is unchanged.
+/// smorph3_pair_backward (float) without the maximum: bound_x (the largest s x the thread's pixels can read) plus
+/// bound_w (the largest s w_k) is at least every u_k of the patch, and the caller has checked that scale * (range of x
+/// in the warp's block + range of w) is small, so that 2^(scale (u_k - bound)) of the taps that carry the weight is far
+/// from underflow. The maximum pass goes, and d_k = u_k - bound costs one packed add per tap on top of four centred
+/// window elements per row. The sums S, sum e d and sum e d^2 are relative to the bound instead of the pixel's own
+/// maximum; everything after them is unchanged.
 __device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __restrict__ win, const float* __restrict__ swk, float* __restrict__ wbin,
                                                               float* __restrict__ abin, float* __restrict__ red, float s, float abs_alpha, float scale,
-                                                              float bound, const float (&grad)[PATCH_H][PATCH_W], int tx, int ty, int lane,
-                                                              float (&gxr)[PATCH_H + 2][PATCH_W + 2])
+                                                              float bound_x, float bound_w, const float (&grad)[PATCH_H][PATCH_W], int tx, int ty,
+                                                              int lane, float (&gxr)[PATCH_H + 2][PATCH_W + 2])
 {
     constexpr int OFF = segment_offset(3, 4), STRIDE = window_stride(3, 4);
-    float2 tap_sum[9];
-    float shifted[9];
+    float2 tap_sum[9], shifted[9];
 #pragma unroll
     for (int k = 0; k < 9; k++)
     {
         tap_sum[k] = make_float2(0.0f, 0.0f);
-        shifted[k] = swk[k] - bound;
+        shifted[k] = make_float2(swk[k] - bound_w, swk[k] - bound_w);
     }
+    const float minus_bound_x = -bound_x;
     float2 alpha_sum = make_float2(0.0f, 0.0f);
     const float2 scale2 = make_float2(scale, scale), alpha2 = make_float2(abs_alpha, abs_alpha), minus_alpha2 = make_float2(-abs_alpha, -abs_alpha);
     const float2 one2 = make_float2(1.0f, 1.0f);
@@ -632,9 +632,13 @@ __device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __res
                 const float* row = win + (ty * PATCH_H + rr + 2 - kh) * STRIDE + tx * PATCH_W + 4 * quad;
                 lds128(seg, row);
                 lds128(seg + 4, row + 4);
+                // d_k = (s x - bound_x) + (s w_k - bound_w): the first difference is exact for the pixels near the bound and
+                // the second is small, so d_k rounds at its own size even when x is far from zero.
+                float centred[4];
 #pragma unroll
-                for (int kw = 0; kw < 3; kw++)
-                    d[kh * 3 + kw] = make_float2(fmaf(s, seg[base + 2 - kw], shifted[kh * 3 + kw]), fmaf(s, seg[base + 3 - kw], shifted[kh * 3 + kw]));
+                for (int i = 0; i < 4; i++) centred[i] = fmaf(s, seg[base + i], minus_bound_x);
+#pragma unroll
+                for (int kw = 0; kw < 3; kw++) d[kh * 3 + kw] = __fadd2_rn(make_float2(centred[2 - kw], centred[3 - kw]), shifted[kh * 3 + kw]);
             }
             float2 sum = make_float2(0.0f, 0.0f), weighted = sum, second = sum;
 #pragma unroll
@@ -1184,7 +1188,7 @@ struct SmorphBackwardArgs
 
 /// 3 x 3 float kernels may skip the maximum (smorph3_pair_backward_bounded) while scale * (range of x in the warp's
 /// block + range of w) stays below this many binades.
-constexpr float BOUND_RANGE = 32.0f;
+constexpr float BOUND_RANGE = 64.0f;
 template <typename T, int KH, int KW, bool SOFT>
 __host__ __device__ constexpr bool backward_bounds() { return sizeof(T) == 4 && !SOFT && KH == 3 && KW == 3; }
 
@@ -1683,7 +1687,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             if (scale * (bound_range + pr.y) <= BOUND_RANGE)
                             {
                                 smorph3_pair_backward_bounded(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale,
-                                                              (s > 0.0f ? local_hi : -local_lo) + pr.x, grad, tx, ty, lane, gxr);
+                                                              s > 0.0f ? local_hi : -local_lo, pr.x, grad, tx, ty, lane, gxr);
                                 done = true;
                             }
                         }

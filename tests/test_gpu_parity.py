@@ -276,18 +276,22 @@ def test_smorph_factorised_forward_matches_double(C, case, merge):
 
 @pytest.mark.parametrize("case", [
     # kernel, image, alphas, spread of x
+    (3, 224, "uniform", 1.0), (3, 97, "per_pair", 1.0), (3, 61, "extreme", 1.0), (3, 130, "per_pair", 30.0), (3, 100, "offset", 1.0),
     (5, 128, "uniform", 1.0), (5, 97, "per_pair", 1.0), (5, 61, "extreme", 1.0), (7, 128, "uniform_negative", 1.0),
     (7, 131, "per_pair", 1.0), (7, 70, "extreme", 3.0), (7, 100, "per_pair", 30.0)])
 @pytest.mark.parametrize("merge", ["sum", "mean", "identity"])
 def test_smorph_factorised_backward_matches_double(C, case, merge):
     """The float backward pass of 5 x 5 and 7 x 7 structuring elements (sum / mean / identity merges) recomputes the
-    sums S and N of a pair from the factorised form wherever the forward pass may use it, and subtracts the maximum
-    elsewhere. Both must agree with the double kernel, which always subtracts the maximum: interior and border
-    blocks, partial tiles, alpha = 0, signs mixed within one input channel, ranges on both sides of the switch."""
+    sums S and N of a pair from the factorised form wherever the ranges allow it, the 3 x 3 one takes its exponentials
+    relative to a bound of the thread's patch instead of the pixel's maximum, and both subtract the maximum elsewhere.
+    All must agree with the double kernel, which always subtracts the maximum: interior and border blocks, partial
+    tiles, alpha = 0, signs mixed within one input channel, ranges on both sides of the switch, inputs far from zero."""
     k, hw, kind, spread = case
     g = torch.Generator().manual_seed(4321 + k + hw)
     co, ci = (6, 6) if merge == "identity" else (6, 5)
     x = (spread * torch.randn((2, ci, hw, hw + 3), generator=g)).cuda()
+    if kind == "offset":   # activations of a deep layer: unit spread around 100
+        x = 100.0 + x
     w = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, k, k), generator=g)).cuda()
     gy = torch.randn((2, co, hw, hw + 3), generator=g).cuda()
     pairs = (co,) if merge == "identity" else (co, ci)
@@ -297,6 +301,8 @@ def test_smorph_factorised_backward_matches_double(C, case, merge):
         a = torch.full(pairs, -8.0)
     elif kind == "per_pair":
         a = 3.0 * torch.randn(pairs, generator=g)
+    elif kind == "offset":
+        a = 2.0 + 0.5 * torch.randn(pairs, generator=g)
     else:
         values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, 1e-4, 3.0, 25.0, 400.0])
         a = values[torch.randint(0, len(values), pairs, generator=g)]
