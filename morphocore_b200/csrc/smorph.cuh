@@ -1560,7 +1560,20 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             local_hi = fmaxf(local_hi, seg[c] < 1e29f ? seg[c] : -Limits<float>::inf());
                         }
                     }
-                    if (x_hi >= x_lo && local_hi >= local_lo) bound_range = x_hi - x_lo;
+                    if constexpr (BOUNDED)
+                    {
+                        // The decision to skip the maximum must be the same for the whole warp (both forms reduce over the
+                        // warp): it rests on the widest range any of its threads sees in its own window, which bounds that
+                        // thread's exponents. A thread whose window lies outside the image reads no tap that counts and
+                        // takes the block's extremes as its (finite) bound.
+                        if (!(local_hi >= local_lo))
+                        {
+                            local_hi = x_hi;
+                            local_lo = x_hi;
+                        }
+                        const float widest = from_ordered(__reduce_max_sync(0xffffffffu, to_ordered(local_hi - local_lo)));
+                        if (x_hi >= x_lo) bound_range = widest;
+                    }
                 }
             }
             T grad[PATCH_H][PATCH_W], next[PATCH_H][PATCH_W];
