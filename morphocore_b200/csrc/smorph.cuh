@@ -1576,12 +1576,21 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                     }
                 }
             }
-            T grad[PATCH_H][PATCH_W], next[PATCH_H][PATCH_W];
-            if (half < oc) load_grad(oc0 + half, grad);
+            // The 3 x 3 float kernel has no registers to spare for the next channel's gradients (it spills at 128): its
+            // loads are covered by the other warps instead.
+            constexpr bool PREFETCH = !(KH == 3 && sizeof(T) == 4);
+            T grad[PATCH_H][PATCH_W];
+            [[maybe_unused]] T next[PREFETCH ? PATCH_H : 1][PREFETCH ? PATCH_W : 1];
+            if constexpr (PREFETCH)
+                if (half < oc) load_grad(oc0 + half, grad);
             for (int oo = half; oo < oc; oo += o_step)
             {
                 const int o = oc0 + oo;
-                if (oo + o_step < oc) load_grad(o + o_step, next);  // the next channel's gradients arrive while this one computes
+                if constexpr (PREFETCH)
+                {
+                    if (oo + o_step < oc) load_grad(o + o_step, next);  // the next channel's gradients arrive while this one computes
+                }
+                else load_grad(o, grad);
                 const T s = spar[oo * 3], abs_alpha = spar[oo * 3 + 1], scale = spar[oo * 3 + 2];
                 const bool neg = s < T(0);
                 const T* win = sx + (neg ? welems : 0);
@@ -1708,10 +1717,13 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                     if (!done) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
                 }
                 else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                if constexpr (PREFETCH)
+                {
 #pragma unroll
-                for (int rr = 0; rr < PATCH_H; rr++)
+                    for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                    for (int j = 0; j < PATCH_W; j++) grad[rr][j] = next[rr][j];
+                        for (int j = 0; j < PATCH_W; j++) grad[rr][j] = next[rr][j];
+                }
             }
         }
         __syncthreads();
