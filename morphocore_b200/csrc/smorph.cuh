@@ -303,10 +303,10 @@ __device__ __forceinline__ void smorph3_pair_backward(const T* __restrict__ win,
 // reciprocal of the smallest possible S, 2^96, is far from overflow.
 constexpr float FACTOR_RANGE = 96.0f;
 // The backward pass multiplies the relative error of the exponentials by |alpha| times the gradient, and s x - Mx rounds
-// at the size of the range: it switches to the max-subtracting statistics earlier.
-constexpr float FACTOR_RANGE_BACKWARD = 80.0f;
-// Exponents beyond this many binades are formed with exp2_product (factor_fill).
-constexpr float FACTOR_PRECISE = 32.0f;
+// at the size of the range: beyond FACTOR_PRECISE binades its tables and its statistics carry the rounding errors of
+// their differences into the exponents (factor_fill, smorph_stats_factored), which lets it use the forward limit.
+constexpr float FACTOR_RANGE_BACKWARD = 96.0f;
+constexpr float FACTOR_PRECISE = 8.0f;
 
 template <int KW>
 struct FactorLayout
@@ -339,13 +339,23 @@ __device__ __forceinline__ float from_ordered(int i) { return __int_as_float(i ^
 /// one fused multiply-add, so the result does not inherit the rounding of a product of magnitude up to FACTOR_RANGE
 /// (half an ulp of 100 is a relative error of 2.6e-6 in the exponential, which the backward pass multiplies by |alpha|).
 /// Excluded window elements (d = -1e30) give 0.
-__device__ __forceinline__ float exp2_product(float d, float scale)
+/// `tail` is a small correction of d (the rounding error of the difference that gave d): 2^((d + tail) * scale).
+__device__ __forceinline__ float exp2_product(float d, float scale, float tail = 0.0f)
 {
-    const float hi = rintf(fmaxf(d * scale, -160.0f));
+    const float product = d * scale;
+    const float hi = rintf(fmaxf(product, -160.0f));
     float e_hi, e_lo;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e_hi) : "f"(hi));
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e_lo) : "f"(fmaf(d, scale, -hi)));
-    return e_hi * e_lo;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e_lo) : "f"(fmaf(tail, scale, fmaf(d, scale, -hi))));
+    return product > -160.0f ? e_hi * e_lo : 0.0f;
+}
+
+/// a + b = sum + error exactly (Knuth's two-sum; the build keeps float arithmetic as written).
+__device__ __forceinline__ void two_sum(float a, float b, float& sum, float& error)
+{
+    sum = a + b;
+    const float bb = sum - a;
+    error = (a - (sum - bb)) + (b - bb);
 }
 
 /// Smallest and largest in-image x of the warp's block (window elements outside the image hold +-1e30 and are
@@ -401,7 +411,13 @@ __device__ __forceinline__ void factor_fill(const float* __restrict__ origin, fl
             float e0, e1, e2, e3;
             if (ALLOW_PRECISE && precise)
             {
-                e0 = exp2_product(x0, scale); e1 = exp2_product(x1, scale); e2 = exp2_product(x2, scale); e3 = exp2_product(x3, scale);
+                // s x - centre rounds at the size of the range: its rounding error goes into the exponent too.
+                float t0, t1, t2, t3, h;
+                two_sum(s * v.x, -centre, h, t0);
+                two_sum(s * v.y, -centre, h, t1);
+                two_sum(s * v.z, -centre, h, t2);
+                two_sum(s * v.w, -centre, h, t3);
+                e0 = exp2_product(x0, scale, t0); e1 = exp2_product(x1, scale, t1); e2 = exp2_product(x2, scale, t2); e3 = exp2_product(x3, scale, t3);
             }
             else
             {
@@ -1267,12 +1283,14 @@ __host__ __device__ constexpr bool backward_factorises() { return backward_split
 /// S' = sum_k 2^(scale (u_k - out_u)) = S 2^(-scale N / S), the sum the gradient pass works with.
 template <int KW>
 __device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__ ea, const float2* __restrict__ eb, int lane, float scale, float base,
-                                                      float shift, const float (&grad)[PATCH_H][PATCH_W], float (&centre)[PATCH_H][PATCH_W],
-                                                      float (&scaled)[PATCH_H][PATCH_W])
+                                                      float shift, float mx, float mw, bool precise, const float (&grad)[PATCH_H][PATCH_W],
+                                                      float (&centre)[PATCH_H][PATCH_W], float (&scaled)[PATCH_H][PATCH_W])
 {
     float2 acc[PATCH_H][PATCH_W];
     float rest[PATCH_H][PATCH_W];
     factor_pair<KW, true>(ea, eb, 1, lane, acc, rest, shift);
+    float ref_hi, ref_lo;   // Mx + Mw without rounding
+    two_sum(mx, mw, ref_hi, ref_lo);
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -1283,9 +1301,19 @@ __device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__
             // out_u = ref + shift + N / S, with `base` = ref + shift formed by the caller without the detour through ref: the
             // quotient is small, so out_u rounds at its own size. out_u - ref (for S') may round at the size of the range.
             const float quotient = (acc[rr][j].y + rest[rr][j]) * inv_sum;
-            const float out_d = acc[rr][j].x > 0.0f ? quotient + shift : 0.0f;   // <= 0
             centre[rr][j] = base + quotient;
-            scaled[rr][j] = grad[rr][j] * (inv_sum * ex2_approx(fminf(scale * out_d, 0.0f)));   // 1 / S' <= 1 first: no overflow
+            // 1 / S' = 2^(scale (out_u - Mx - Mw)) / S, a factor of every c_k of the pixel: its exponent has to be as exact
+            // as the float out_u the gradient pass will use. Beyond a few binades (`precise`, warp uniform) the difference is
+            // taken without rounding (two-sum) and its tail goes into the exponent.
+            float factor;
+            if (precise)
+            {
+                float z, tail;
+                two_sum(centre[rr][j], -ref_hi, z, tail);
+                factor = exp2_product(fminf(z, 0.0f), scale, tail - ref_lo);
+            }
+            else factor = ex2_approx(fminf(scale * (quotient + shift), 0.0f));
+            scaled[rr][j] = grad[rr][j] * (inv_sum * factor);   // 1 / S' <= 1 first: no overflow
         }
 }
 
@@ -1690,7 +1718,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                                 }
                                 // The thread's own largest s x: centre of its linear sums, and with Mw the base of its soft extrema.
                                 const float local = local_hi >= local_lo ? (s > 0.0f ? local_hi : -local_lo) : held_centre;
-                                smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, local + pr.x, local - held_centre, grad, centre, scaled);
+                                smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, local + pr.x, local - held_centre, held_centre, pr.x,
+                                                           scale * (x_hi - x_lo) > FACTOR_PRECISE, grad, centre, scaled);
                                 have_stats = true;
                             }
                         }
