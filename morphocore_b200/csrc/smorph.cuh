@@ -1277,10 +1277,12 @@ template <typename T, int KH, int KW, bool SOFT>
 __host__ __device__ constexpr bool backward_factorises() { return backward_splits<T, KH, KW>() && !SOFT; }
 
 /// Statistics of one pair from the factorised form (see "Factorised forward"): `ea` holds (E, A) of the warp's block for
-/// this pair's sign and scale, `eb` the pair's (Ew, Bw), and ref = Mx + Mw bounds every u_k from above. factor_pair
-/// gives S = sum_k 2^(scale (u_k - ref)) and N = sum_k 2^(scale (u_k - ref)) (u_k - ref) in three fused multiply-adds
-/// per tap, no maximum and no exponential (N is summed relative to `shift`, see factor_pair). Out: centre = out_u = ref + N / S and scaled = g / S' with
-/// S' = sum_k 2^(scale (u_k - out_u)) = S 2^(-scale N / S), the sum the gradient pass works with.
+/// this pair's sign and scale, `eb` the pair's (Ew, Bw), and ref = mx + mw (the block's largest s x plus the largest
+/// s w_k) bounds every u_k from above. factor_pair gives S = sum_k 2^(scale (u_k - ref)) and
+/// N = sum_k 2^(scale (u_k - ref)) (u_k - ref - shift) in three fused multiply-adds per tap, no maximum and no
+/// exponential; `shift` (<= 0) is the thread's own largest s x minus mx, and `base` = ref + shift formed directly.
+/// Out: centre = out_u = base + N / S, and scaled = g / S' with S' = sum_k 2^(scale (u_k - out_u)) = S 2^(scale (ref - out_u)),
+/// the sum the gradient pass works with.
 template <int KW>
 __device__ __forceinline__ void smorph_stats_factored(const float4* __restrict__ ea, const float2* __restrict__ eb, int lane, float scale, float base,
                                                       float shift, float mx, float mw, bool precise, const float (&grad)[PATCH_H][PATCH_W],
