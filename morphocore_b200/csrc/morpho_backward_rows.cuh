@@ -90,17 +90,17 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_rows_kernel(
 
         // Pass 1: best value and the first kernel row that attains it.
         T best[OB][PATCH_H][PATCH_W];
-        int row[OB][PATCH_H][PATCH_W];
+        unsigned int row[PATCH_H][PATCH_W];   // byte o: the first kernel row that attains best[o] (one register for the four channels)
+        static_assert(OB <= 4 && KW < 256, "one byte per channel");
 #pragma unroll
-        for (int o = 0; o < OB; o++)
+        for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-            for (int rr = 0; rr < PATCH_H; rr++)
+            for (int j = 0; j < PATCH_W; j++)
+            {
+                row[rr][j] = 0u;
 #pragma unroll
-                for (int j = 0; j < PATCH_W; j++)
-                {
-                    best[o][rr][j] = op_init;
-                    row[o][rr][j] = 0;
-                }
+                for (int o = 0; o < OB; o++) best[o][rr][j] = op_init;
+            }
 #pragma unroll
         for (int kh = 0; kh < KW; kh++)
         {
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_rows_kernel(
                         if (strictly_better<IS_MIN>(rb, best[o][rr][j]))
                         {
                             best[o][rr][j] = rb;
-                            row[o][rr][j] = kh;
+                            row[rr][j] = (row[rr][j] & ~(0xffu << (8 * o))) | (static_cast<unsigned int>(kh) << (8 * o));
                         }
                     }
         }
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_rows_kernel(
                 {
                     const T v = grad[o][rr][j];
                     if (v == T(0)) continue;
-                    int kh = row[o][rr][j], kw = 0;
+                    int kh = static_cast<int>((row[rr][j] >> (8 * o)) & 0xffu), kw = 0;
                     const T target = best[o][rr][j];
                     if (target != op_init)
                     {
