@@ -38,7 +38,8 @@ METRIC = "fwd+bwd Gtaps/s"
 UNIT = "Gtaps/s"
 
 # Roofline denominators in Gtaps/s: instruction-mix ceilings of the CUDA cores, measured LIVE at the start of
-# the run by morphocore_b200/probe_rates (register-only kernels, every operand loop carried). The values
+# the run by ./probe_rates (source probe_rates.cu: register-only kernels, every operand loop carried, the SM clock
+# sampled inside each kernel). The values
 # below are an earlier measurement on this pool's B200 (profiles/probe_rates_b200.md), used only when the
 # probe binary is missing. A dilation / erosion tap is one add and one max; the float peak is the best mix
 # found (packed add.f32x2 + 3-input max), the double peak DADD + compare/select; a smorph tap costs three
@@ -50,7 +51,7 @@ PEAK_SOURCE = "earlier measurement on this pool (probe binary missing)"
 def measure_peaks():
     """Run the instruction-rate probe on the current GPU and fill PEAK_GTAPS; returns the raw rates."""
     global PEAK_SOURCE
-    exe = os.path.join(ROOT, "morphocore_b200", "probe_rates")
+    exe = os.path.join(ROOT, "probe_rates")
     if not os.path.exists(exe):
         return None
     try:
@@ -61,8 +62,9 @@ def measure_peaks():
         # smorph forward (sum / mean / identity merges): the factorised kernel needs 3 fused multiply-adds per tap and
         # no exponential; smorph backward: 11 FP32 operations (u, d, scale, sum e, e d, sum e d, sum e d^2, two for c_k,
         # grad_input and grad_weight accumulation) and one ex2 per tap.
-        PEAK_GTAPS["smorph_fwd_f32"] = r["fma_ops"] / 3
-        PEAK_GTAPS["smorph_bwd_f32"] = min(r["ex2_ops"], r["fma_ops"] / 11)
+        fma = max(r["fma_ops"], r.get("fma2_ops", 0.0))
+        PEAK_GTAPS["smorph_fwd_f32"] = fma / 3
+        PEAK_GTAPS["smorph_bwd_f32"] = min(r["ex2_ops"], fma / 11)
         PEAK_GTAPS["smorph_fwdbwd_f32"] = 1.0 / (1.0 / PEAK_GTAPS["smorph_fwd_f32"] + 1.0 / PEAK_GTAPS["smorph_bwd_f32"])
         PEAK_SOURCE = "of measured (instruction-rate probe run on this GPU at the start of this bench)"
         return r

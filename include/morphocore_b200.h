@@ -8,11 +8,16 @@
  * Conventions
  *  - Every pointer is a device pointer on the device that is current when the call is made, tensors are
  *    contiguous NCHW (input, output, gradients) or OIHW (structuring element), float32 or float64.
- *  - The functions never allocate, free or synchronise: work is queued on `stream` (a cudaStream_t
- *    passed as void*, NULL = the legacy default stream), scratch memory is passed in by the caller.
+ *  - The compute functions never allocate, free or synchronise: work is queued on `stream` (a cudaStream_t
+ *    passed as void*, NULL = the legacy default stream), scratch memory is passed in by the caller. The one
+ *    exception is mc_morpho_backward_noalloc, whose scratch is an array inside the library (see there).
  *  - The return value is MC_OK or a negative mc_status; mc_status_string() names it and
  *    mc_last_error() gives the detail of the last failure of the calling thread.
- *  - Re-entrant and thread safe; the only process state is the per-kernel shared-memory opt-in.
+ *  - The compute functions are re-entrant and thread safe, except mc_morpho_backward_noalloc, whose calls on one
+ *    device share one scratch array. Process state: the per-kernel shared-memory opt-in, the wait limit
+ *    (mc_set_wait_limit_ns), the launch counter and, per device, the counter of timed-out waits
+ *    (mc_device_error_count), which hosts should poll at their own synchronisation points: a thread block whose
+ *    wait ran out returns without writing its tile, and the call that launched it has long returned MC_OK.
  */
 #ifndef MORPHOCORE_B200_H
 #define MORPHOCORE_B200_H
@@ -136,6 +141,18 @@ const char* mc_last_error(void);
  * asynchronous (TMA) copy ran out and which therefore returned early: 0 in a healthy run. Synchronises
  * the device; negative mc_status on failure. No counterpart in the reference (its kernels do not wait). */
 int mc_device_error_count(void);
+
+/* Sets the counter read by mc_device_error_count back to zero on the current device. */
+int mc_device_error_reset(void);
+
+/* Time limit, in nanoseconds of the GPU's global timer, of every wait on an asynchronous copy in kernels launched
+ * from now on (default 1 s). No counterpart in the reference. */
+int mc_set_wait_limit_ns(uint64_t limit_ns);
+
+/* Self-test of the time-out path: queues one thread block that waits, with the same bounded wait as the kernels,
+ * for a copy that is never issued. After limit_ns (at most 1 s) it gives up, adds one to the counter of
+ * mc_device_error_count and returns; the context stays usable. No counterpart in the reference. */
+int mc_selftest_wait_timeout(uint64_t limit_ns, void* stream);
 
 /* Number of kernels this library has launched in the calling process since it was loaded. */
 uint64_t mc_launch_count(void);

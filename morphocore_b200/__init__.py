@@ -9,5 +9,6 @@ __version__ = "0.1.0"
 
 from . import _native  # noqa: F401  (loads the C-ABI library and registers torch.ops.morphocore)
 from . import functional, nn  # noqa: F401
+from ._native import device_error_count  # noqa: F401
 
-__all__ = ["functional", "nn", "__version__"]
+__all__ = ["functional", "nn", "device_error_count", "__version__"]

@@ -3,7 +3,7 @@
   morphocore_b200/libmorphocore_b200.so   CUDA kernels + the C-ABI of include/morphocore_b200.h (nvcc)
   morphocore_b200/_C.so                   thin PyTorch C++ extension registering torch.ops.morphocore.* (g++)
 
-Usage: python -m morphocore_b200.build [--force] [--verbose]   (does not import the package's operators)
+Usage: python morphocore_b200/build.py [--force] [--verbose]   (run by path: it must work before the libraries exist)
 """
 import argparse
 import os
@@ -82,7 +82,8 @@ def build_ext(force=False, verbose=False):
 
 def build_probe(force=False, verbose=False):
     """The instruction-rate probe bench.py runs for its roofline denominators (a stand-alone executable)."""
-    src, out = os.path.join(CSRC, "probe_rates.cu"), os.path.join(PKG, "probe_rates")
+    root = os.path.dirname(PKG)
+    src, out = os.path.join(root, "probe_rates.cu"), os.path.join(root, "probe_rates")
     if not force and _newer(out, [src]):
         return out
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

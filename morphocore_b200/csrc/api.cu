@@ -28,6 +28,31 @@ unsigned int* device_error_counter()
     return p;
 }
 
+static std::atomic<uint64_t> g_wait_limit_ns{1000000000ull};  // one second
+
+uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+
+/// One CTA that waits, with the bounded wait of the TMA kernels, on an mbarrier that expects 16 bytes which no copy
+/// ever delivers: the wait runs out after limit_ns, the CTA counts the time-out and returns. Nothing faults or
+/// spins; this is how the time-out path is exercised.
+__global__ void wait_timeout_selftest_kernel(unsigned int* errors, uint64_t limit_ns)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0)
+    {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_expect_tx(&bar, 16);
+    __syncthreads();
+    if (!mbar_wait(&bar, 0, limit_ns))
+    {
+        if (threadIdx.x == 0 && errors != nullptr) atomicAdd(errors, 1u);
+        return;
+    }
+}
+
 static thread_local char g_last_error[512] = "";
 static std::atomic<uint64_t> g_launches{0};
 
@@ -43,13 +68,24 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 /// Checks shared by every entry point. The limits on taps and channels are those of the packed winner
 /// index, (channel << 16) | tap.
-static int validate(const mc_desc* d, bool morph, bool smooth = false)
+int validate(const mc_desc* d, bool morph, bool smooth)
 {
     if (d == nullptr) { set_last_error("descriptor is NULL"); return MC_ERR_INVALID_ARGUMENT; }
     if (d->B < 0 || d->Ci <= 0 || d->Co <= 0 || d->H < 0 || d->W < 0 || d->kH <= 0 || d->kW <= 0)
     {
         set_last_error("sizes must be positive (B=%d Ci=%d Co=%d H=%d W=%d kH=%d kW=%d)", d->B, d->Ci, d->Co, d->H, d->W, d->kH, d->kW);
         return MC_ERR_INVALID_ARGUMENT;
+    }
+    {
+        // Element counts must stay far inside 64 bits (the workspace sizes multiply four extents): 2^40 elements is
+        // more than any device holds.
+        const unsigned __int128 limit = static_cast<unsigned __int128>(1) << 40;
+        const unsigned __int128 pixels = static_cast<unsigned __int128>(d->B) * static_cast<unsigned>(d->H) * static_cast<unsigned>(d->W);
+        if (pixels * static_cast<unsigned>(d->Ci) > limit || pixels * static_cast<unsigned>(d->Co) > limit)
+        {
+            set_last_error("tensor of more than 2^40 elements (B=%d Ci=%d Co=%d H=%d W=%d)", d->B, d->Ci, d->Co, d->H, d->W);
+            return MC_ERR_INVALID_ARGUMENT;
+        }
     }
     if (d->dtype != MC_F32 && d->dtype != MC_F64) { set_last_error("unknown dtype %d", d->dtype); return MC_ERR_INVALID_ARGUMENT; }
     if (d->merge < MC_MERGE_MAX || d->merge > MC_MERGE_IDENTITY) { set_last_error("Unknown merge mode %d", d->merge); return MC_ERR_INVALID_ARGUMENT; }
@@ -274,12 +310,47 @@ const char* mc_last_error(void) { return g_last_error; }
 int mc_device_error_count(void)
 {
     unsigned int count = 0;
-    if (cudaMemcpyFromSymbol(&count, g_device_error, sizeof(count)) != cudaSuccess)
+    const cudaError_t err = cudaMemcpyFromSymbol(&count, g_device_error, sizeof(count));
+    if (err != cudaSuccess)
     {
-        set_last_error("cudaMemcpyFromSymbol: %s", cudaGetErrorString(cudaGetLastError()));
+        set_last_error("cudaMemcpyFromSymbol: %s", cudaGetErrorString(err));
         return MC_ERR_CUDA;
     }
-    return static_cast<int>(count);
+    return static_cast<int>(count > 0x7fffffffu ? 0x7fffffffu : count);
+}
+
+int mc_device_error_reset(void)
+{
+    const unsigned int zero = 0;
+    const cudaError_t err = cudaMemcpyToSymbol(g_device_error, &zero, sizeof(zero));
+    if (err != cudaSuccess)
+    {
+        set_last_error("cudaMemcpyToSymbol: %s", cudaGetErrorString(err));
+        return MC_ERR_CUDA;
+    }
+    return MC_OK;
+}
+
+int mc_set_wait_limit_ns(uint64_t limit_ns)
+{
+    if (limit_ns == 0)
+    {
+        set_last_error("the wait limit must be positive");
+        return MC_ERR_INVALID_ARGUMENT;
+    }
+    g_wait_limit_ns.store(limit_ns, std::memory_order_relaxed);
+    return MC_OK;
+}
+
+int mc_selftest_wait_timeout(uint64_t limit_ns, void* stream)
+{
+    if (limit_ns == 0 || limit_ns > 1000000000ull)
+    {
+        set_last_error("mc_selftest_wait_timeout: limit of 1 ns .. 1 s expected");
+        return MC_ERR_INVALID_ARGUMENT;
+    }
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_error_counter(), limit_ns);
+    return check_launch("wait_timeout_selftest_kernel");
 }
 
 uint64_t mc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -249,6 +249,10 @@ __device__ __forceinline__ T read_border(const T* __restrict__ plane, const Geom
 void set_last_error(const char* fmt, ...);
 void count_launch();
 
+/// Checks shared by every entry point (sizes, enums, identity shape, index limits); `morph` selects the dilation /
+/// erosion fields, `smooth` the smooth-merge entry points. MC_OK or a negative status with the message set.
+int validate(const mc_desc* d, bool morph, bool smooth = false);
+
 /// Opt in to more than 48 KiB of dynamic shared memory for a kernel; returns false if the device refuses.
 template <typename K> inline bool allow_shared(K kernel, size_t bytes)
 {

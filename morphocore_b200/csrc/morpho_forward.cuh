@@ -38,6 +38,7 @@ struct ForwardArgs
     int chunk;      // input channels staged per barrier
     bool vec_store; // y rows are 16-byte aligned
     unsigned int* errors;  // counter of timed-out waits
+    uint64_t wait_limit_ns; // bound of one wait on a TMA copy
 };
 
 template <int OB, typename T>
@@ -300,7 +301,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
         stage_weights<T, IS_MIN, OB>(sw, wb, g, o0, c0, cc);
         if constexpr (USE_TMA)
         {
-            if (!mbar_wait(full + (n & 1), (n >> 1) & 1))
+            if (!mbar_wait(full + (n & 1), (n >> 1) & 1, a.wait_limit_ns))
             {
                 if (threadIdx.x == 0 && a.errors != nullptr) atomicAdd(a.errors, 1u);
                 return;  // every thread of the CTA waits on the same barrier and gives up together
@@ -518,6 +519,7 @@ int launch_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx,
     }
     const bool track = idx != nullptr;
     a.errors = device_error_counter();
+    a.wait_limit_ns = wait_limit_ns();
 
     // TMA staging when the tensor can be described by a tensor map (16-byte row pitch and base).
     ForwardPlan<T> plan;

@@ -65,11 +65,10 @@ int scratch_address(void** out)
 
 extern "C" int mc_morpho_backward_noalloc(const mc_desc* desc, const void* x, const void* w, const void* gy, void* gx, void* gw, void* stream)
 {
-    if (desc == nullptr)
-    {
-        mc::set_last_error("descriptor is NULL");
-        return MC_ERR_INVALID_ARGUMENT;
-    }
+    // The descriptor is checked before anything is sized from it: a negative extent must read "invalid argument",
+    // not a wrapped-around pixel count.
+    const int valid = mc::validate(desc, true);
+    if (valid != MC_OK) return valid;
     const size_t need = mc_morpho_backward_workspace_bytes(desc, 0);
     if (need > SCRATCH_BYTES)
     {

@@ -724,6 +724,7 @@ struct SmorphForwardArgs
     int chunk;
     int factorise;    // use the factorised path where it is safe (merges without winner test)
     unsigned int* errors;  // counter of timed-out waits
+    uint64_t wait_limit_ns; // bound of one wait on a TMA copy
 };
 
 /// CTA = (batch element, group of OB output channels, tile), looping over chunks of input channels; with
@@ -961,7 +962,7 @@ __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 1 : 2)
         }
         if constexpr (USE_TMA)
         {
-            if (!mbar_wait(full + (n & 1), (n >> 1) & 1))
+            if (!mbar_wait(full + (n & 1), (n >> 1) & 1, a.wait_limit_ns))
             {
                 if (threadIdx.x == 0 && a.errors != nullptr) atomicAdd(a.errors, 1u);
                 return;  // every thread of the CTA waits on the same barrier and gives up together
@@ -1131,6 +1132,7 @@ int launch_smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alp
     a.beta = beta; a.soft_ref = soft_ref; a.soft_inv = soft_inv;
     a.o_groups = (d.Co + OB - 1) / OB;
     a.errors = device_error_counter();
+    a.wait_limit_ns = wait_limit_ns();
     const int channels = a.g.identity ? 1 : d.Ci;
     const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * a.o_groups * d.B;
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }

@@ -1,8 +1,8 @@
 // TMA staging of tile windows: tensor-map creation on the host, mbarrier and cp.async.bulk.tensor wrappers
 // on the device. One 4-D tiled copy (no multicast) brings the windows of a whole chunk of input channels
 // of one tile into shared memory, out-of-image elements zero filled, while the CTA computes on the
-// previous chunk. Every wait on an mbarrier is bounded: when it runs out the kernel records the fact in
-// g_device_error and returns instead of spinning.
+// previous chunk. Every wait on an mbarrier is bounded in time (the device's global timer): when it runs out the
+// kernel records the fact in g_device_error and returns instead of spinning.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -67,12 +67,25 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 
-/// Bounded wait for the phase with the given parity. Each try suspends for a hardware-limited time; the
-/// loop gives up after about a second and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+/// Nanoseconds a kernel waits for one TMA copy before it gives up (host side; mc_set_wait_limit_ns changes it, the
+/// launchers copy it into the kernel arguments).
+uint64_t wait_limit_ns();
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+/// Bounded wait for the phase with the given parity: tries until `limit_ns` nanoseconds of the device's global
+/// timer have passed since the first failed try, then returns false. The timer is only read once a try has failed,
+/// so a copy that has already landed costs one try.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns)
 {
     const uint32_t addr = smem_addr(bar);
-    for (int it = 0; it < (1 << 22); it++)
+    uint64_t start = 0;
+    for (;;)
     {
         uint32_t done;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
@@ -80,8 +93,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
                      : "r"(addr), "r"(parity)
                      : "memory");
         if (done) return true;
+        const uint64_t now = global_timer_ns();
+        if (start == 0) start = now;
+        else if (now - start > limit_ns) return false;
     }
-    return false;
 }
 
 /// 4-D tiled TMA load (no multicast) of the box at (x, y, c, b) into shared memory; completion is

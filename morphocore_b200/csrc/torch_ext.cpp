@@ -210,6 +210,9 @@ public:
         require_cuda(input, "input");
         require_cuda(weight, "weight");
         require_cuda(alpha, "alpha");
+        TORCH_CHECK(weight.device() == input.device() && alpha.device() == input.device(),
+                    "input, weight and alpha must be on the same device (input on ", input.device(), ", weight on ", weight.device(),
+                    ", alpha on ", alpha.device(), ")");
         TORCH_CHECK(input.scalar_type() == weight.scalar_type() && input.scalar_type() == alpha.scalar_type(),
                     "input, weight and alpha must have the same dtype");
         const bool identity = merge == MC_MERGE_IDENTITY;
@@ -252,6 +255,7 @@ public:
         TORCH_CHECK(grad_output.sizes() == output.sizes(), "grad_output shape mismatch: expected [", output.sizes(), "] but got [",
                     grad_output.sizes(), "]");
         TORCH_CHECK(grad_output.scalar_type() == input.scalar_type(), "grad_output must have the same dtype as input");
+        TORCH_CHECK(grad_output.device() == input.device(), "grad_output must be on the same device as input");
 
         const c10::cuda::CUDAGuard device_guard(input.device());
         const mc_desc d = make_desc(input, weight, MC_OP_DILATION, merge);
@@ -291,6 +295,9 @@ public:
         require_cuda(weight, "weight");
         require_cuda(alpha, "alpha");
         require_cuda(beta, "beta");
+        TORCH_CHECK(weight.device() == input.device() && alpha.device() == input.device() && beta.device() == input.device(),
+                    "input, weight, alpha and beta must be on the same device (input on ", input.device(), ", weight on ", weight.device(),
+                    ", alpha on ", alpha.device(), ", beta on ", beta.device(), ")");
         TORCH_CHECK(input.scalar_type() == weight.scalar_type() && input.scalar_type() == alpha.scalar_type()
                         && input.scalar_type() == beta.scalar_type(),
                     "input, weight, alpha and beta must have the same dtype");
@@ -325,6 +332,7 @@ public:
         TORCH_CHECK(grad_output.sizes() == output.sizes(), "grad_output shape mismatch: expected [", output.sizes(), "] but got [",
                     grad_output.sizes(), "]");
         TORCH_CHECK(grad_output.scalar_type() == input.scalar_type(), "grad_output must have the same dtype as input");
+        TORCH_CHECK(grad_output.device() == input.device(), "grad_output must be on the same device as input");
 
         const c10::cuda::CUDAGuard device_guard(input.device());
         const mc_desc d = make_desc(input, weight, MC_OP_DILATION, MC_MERGE_SMOOTH);

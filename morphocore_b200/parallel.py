@@ -46,12 +46,27 @@ class GradBucket:
     def zero(self):
         self.flat.zero_()
 
+    def check_views(self):
+        """Every parameter's .grad must still be its view into the flat buffer. optimizer.zero_grad() with
+        torch's default set_to_none=True (or any code that rebinds p.grad) breaks the alias: the all-reduce would
+        then sum a stale buffer while the optimizer steps on gradients no rank has shared."""
+        offset = 0
+        for n, p in enumerate(self.params):
+            want = self.flat.data_ptr() + offset * self.flat.element_size()
+            if p.grad is None or p.grad.data_ptr() != want or p.grad.numel() != p.numel():
+                raise RuntimeError(
+                    f"GradBucket: the gradient of parameter {n} is no longer a view of the flat buffer "
+                    "(optimizer.zero_grad(set_to_none=True) or a rebound .grad); clear gradients with bucket.zero() "
+                    "or zero_grad(set_to_none=False)")
+            offset += p.numel()
+
     def world_size(self):
         return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
 
     def all_reduce(self, average: bool = True):
         """Sum the buffer over the ranks (mean with `average`). Every rank must call it with a buffer of
         the same length; a mismatch is reported on the host before any collective runs."""
+        self.check_views()
         world = self.world_size()
         if world == 1:
             return

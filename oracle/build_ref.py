@@ -7,7 +7,8 @@ under torch.ops.morphocore when loaded with torch.ops.load_library, so it must n
 process that also imports morphocore_b200 (both own that operator namespace): the golden-vector
 generator and the CPU-baseline runner each use it in a process of their own.
 
-Usage: python oracle/build_ref.py [--reference /path/to/reference] [--force]
+Usage: python oracle/build_ref.py --reference /path/to/reference [--force]
+(or set MORPHOCORE_REFERENCE to the root of the reference checkout)
 """
 import argparse
 import os
@@ -23,10 +24,22 @@ CPP_DIR = "morphocore/functional/csrc/cpp"
 UNITS = ["morpho_op.cpp", "reshaper.cpp", "smorph.cpp", "bindings.cpp", "smorph_scm.cpp"]
 
 
-def build(reference="/root/reference", force=False, verbose=True):
-    """Return the path of the built library, or None when the reference sources are absent."""
-    src_dir = os.path.join(reference, CPP_DIR)
-    if not os.path.isdir(src_dir):
+def reference_root(explicit=None):
+    """Root of the reference checkout: the argument, else the MORPHOCORE_REFERENCE environment variable, else a
+    folder named `reference` beside this repository; None when none of them holds the sources."""
+    candidates = [explicit, os.environ.get("MORPHOCORE_REFERENCE"),
+                  os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for root in candidates:
+        if root and os.path.isdir(os.path.join(root, CPP_DIR)):
+            return root
+    return None
+
+
+def build(reference=None, force=False, verbose=True):
+    """Return the path of the built library, or None when neither the reference sources nor an earlier build exist."""
+    reference = reference_root(reference)
+    src_dir = os.path.join(reference, CPP_DIR) if reference else None
+    if src_dir is None:
         return OUT_LIB if os.path.exists(OUT_LIB) else None
     if os.path.exists(OUT_LIB) and not force:
         newest = max(os.path.getmtime(os.path.join(src_dir, f)) for f in os.listdir(src_dir))
@@ -70,7 +83,7 @@ def build(reference="/root/reference", force=False, verbose=True):
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=None)
     parser.add_argument("--force", action="store_true")
     args = parser.parse_args()
     path = build(args.reference, args.force)

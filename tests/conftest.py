@@ -45,3 +45,18 @@ def golden():
         return cache[name]
 
     return load
+
+
+@pytest.fixture(scope="session", autouse=True)
+def no_timed_out_waits_at_the_end(request):
+    """After the last GPU test: no thread block of the session gave up on a TMA copy (tests that provoke a
+    time-out on purpose reset the counter themselves)."""
+    yield
+    try:
+        import torch
+        if not torch.cuda.is_available() or "morphocore_b200" not in sys.modules:
+            return
+    except Exception:
+        return
+    import morphocore_b200
+    assert morphocore_b200.device_error_count() == 0, "a bounded wait on a TMA copy timed out during the session"

@@ -9,7 +9,8 @@ Run once, in a process of its own, where the reference sources are available:
 Every fixture stores the inputs next to the reference's outputs, so the tests need neither the
 reference nor a particular RNG. Full-size benchmark configurations are too large to store: for those
 the inputs come from workloads.py (seeded) and the fixture keeps a SHA-256 of the forward output
-bytes, the full weight / alpha gradients and the input gradient at sampled positions.
+bytes, the full weight / alpha gradients and the input gradient at sampled positions (set "full_size";
+the backward pass of config 4 at its full size is the set "cfg4_full").
 """
 import hashlib
 import json
@@ -222,6 +223,25 @@ def full_size_cases():
     return arrays, manifest
 
 
+def cfg4_full_cases():
+    """Config 4 at its full size (8, 64, 512, 512), backward: the whole weight gradient and the input gradient at
+    sampled positions, for both operations."""
+    arrays, manifest = {}, []
+    for op in ("dilation", "erosion"):
+        c = WL.cfg4(op)
+        f = R.dilation if op == "dilation" else R.erosion
+        xr, wr = c["x"].clone().requires_grad_(True), c["w"].clone().requires_grad_(True)
+        y = f(xr, wr, "identity")
+        y.backward(c["gy"])
+        pos = sample_positions(xr.numel(), 8192, seed=13)
+        arrays[f"cfg4_{op}_gw"] = wr.grad.numpy()
+        arrays[f"cfg4_{op}_gx_pos"] = pos
+        arrays[f"cfg4_{op}_gx_val"] = xr.grad.numpy().reshape(-1)[pos]
+        manifest.append(dict(key=f"cfg4_{op}", y_sha256=sha(y.detach().numpy()), gx_sha256=sha(xr.grad.numpy())))
+        del xr, wr, y
+    return arrays, manifest
+
+
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
     # Without arguments every set is regenerated; otherwise only the named ones (the manifest keeps the others).
@@ -230,7 +250,8 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and os.path.exists(manifest_path):
         with open(manifest_path) as f:
             out = json.load(f)
-    for name, fn in (("morph_small", morph_cases), ("smorph_small", smorph_cases), ("scm_small", scm_cases), ("full_size", full_size_cases)):
+    for name, fn in (("morph_small", morph_cases), ("smorph_small", smorph_cases), ("scm_small", scm_cases), ("full_size", full_size_cases),
+                     ("cfg4_full", cfg4_full_cases)):
         if len(sys.argv) > 1 and name not in sys.argv[1:]:
             continue
         arrays, manifest = fn()

@@ -12,7 +12,7 @@ from conftest import ROOT
 @pytest.fixture(scope="module")
 def lib():
     path = os.path.join(ROOT, "morphocore_b200", "libmorphocore_b200.so")
-    assert os.path.exists(path), "build the library with `python -m morphocore_b200.build`"
+    assert os.path.exists(path), "build the library with `python morphocore_b200/build.py`"
     handle = ctypes.CDLL(path)
     handle.mc_status_string.restype = ctypes.c_char_p
     handle.mc_last_error.restype = ctypes.c_char_p
@@ -77,6 +77,14 @@ def test_validation_happens_before_any_launch(lib):
     assert lib.mc_morpho_forward(ctypes.byref(desc(kH=300, kW=300)), one, one, one, None, None) == -2
     assert lib.mc_morpho_forward(ctypes.byref(desc()), None, one, one, None, None) == -1
     assert lib.mc_smorph_forward(ctypes.byref(desc(weight_batch_stride=5)), one, one, one, one, None) == -1
+    # the entry point with built-in scratch validates before it sizes anything from the descriptor
+    assert lib.mc_morpho_backward_noalloc(ctypes.byref(desc(B=-1, merge=0)), one, one, one, one, one, None) == -1
+    assert b"sizes must be positive" in lib.mc_last_error()
+    assert lib.mc_morpho_backward_noalloc(ctypes.byref(desc(merge=9)), one, one, one, one, one, None) == -1
+    assert lib.mc_morpho_forward(ctypes.byref(desc(B=2**20, Co=2**20, H=2**20, W=2**20)), one, one, one, None, None) == -1
+    assert b"2^40" in lib.mc_last_error()
+    lib.mc_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
+    assert lib.mc_set_wait_limit_ns(0) == -1 and lib.mc_set_wait_limit_ns(10**9) == 0
     # an empty batch is a valid no-op
     assert lib.mc_morpho_forward(ctypes.byref(desc(B=0)), None, None, None, None, None) == 0
     assert lib.mc_launch_count() == 0

@@ -27,7 +27,7 @@ def test_public_api_matches_golden_gradients(F, manifest, golden):
         y = fn(x, w, case["merge"], case["padding"], padding_value=case["padding_value"])
         assert np.array_equal(y.detach().cpu().numpy(), data[k + "_y"])
         y.backward(torch.from_numpy(data[k + "_gy"]).cuda())
-        tol = dict(rtol=1e-4, atol=1e-4) if x.dtype == torch.float32 else dict(rtol=1e-11, atol=1e-11)
+        tol = dict(rtol=1e-4, atol=1e-4) if x.dtype == torch.float32 else dict(rtol=1e-12, atol=1e-12)
         np.testing.assert_allclose(x.grad.cpu().numpy(), data[k + "_gx"], **tol)
         np.testing.assert_allclose(w.grad.cpu().numpy(), data[k + "_gw"], **tol)
     data = golden("smorph_small")
@@ -38,8 +38,8 @@ def test_public_api_matches_golden_gradients(F, manifest, golden):
         x, w, a = (torch.from_numpy(data[k + n]).cuda().requires_grad_(True) for n in ("_x", "_w", "_alpha"))
         y = F.smorph(x, w, a, channel_merge_mode=case["merge"])
         y.backward(torch.from_numpy(data[k + "_gy"]).cuda())
-        tol = dict(rtol=1e-4, atol=3e-4) if x.dtype == torch.float32 else dict(rtol=1e-9, atol=1e-10)
-        np.testing.assert_allclose(y.detach().cpu().numpy(), data[k + "_y"], rtol=tol["rtol"], atol=1e-5 if x.dtype == torch.float32 else 1e-11)
+        tol = dict(rtol=1e-4, atol=3e-4) if x.dtype == torch.float32 else dict(rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(y.detach().cpu().numpy(), data[k + "_y"], rtol=tol["rtol"], atol=1e-5 if x.dtype == torch.float32 else 1e-12)
         np.testing.assert_allclose(x.grad.cpu().numpy(), data[k + "_gx"], **tol)
         np.testing.assert_allclose(w.grad.cpu().numpy(), data[k + "_gw"], **tol)
         np.testing.assert_allclose(a.grad.cpu().numpy(), data[k + "_galpha"], rtol=tol["rtol"], atol=tol["atol"] * 10)
@@ -83,8 +83,8 @@ def test_smorph_scm_matches_golden_and_gradcheck(F, manifest, golden):
         y.backward(torch.from_numpy(data[k + "_gy"]).cuda())
         f32 = x.dtype == torch.float32
         big = abs(case["beta0"]) >= 50
-        tol = dict(rtol=1e-3 if big else 1e-4, atol=(3e-3 if big else 3e-4)) if f32 else dict(rtol=1e-8, atol=1e-9)
-        np.testing.assert_allclose(y.detach().cpu().numpy(), data[k + "_y"], rtol=1e-4 if f32 else 1e-10, atol=1e-5 if f32 else 1e-11, err_msg=str(case))
+        tol = dict(rtol=1e-3 if big else 1e-4, atol=(3e-3 if big else 3e-4)) if f32 else dict(rtol=1e-11, atol=1e-11)
+        np.testing.assert_allclose(y.detach().cpu().numpy(), data[k + "_y"], rtol=1e-4 if f32 else 1e-12, atol=1e-5 if f32 else 1e-12, err_msg=str(case))
         for name, t in (("gx", x), ("gw", w), ("galpha", a), ("gbeta", b)):
             want = data[k + "_" + name]
             np.testing.assert_allclose(t.grad.cpu().numpy(), want, rtol=tol["rtol"], atol=tol["atol"] * max(1.0, float(np.abs(want).max())),
@@ -181,23 +181,31 @@ def build_cfg5(device="cuda"):
 
 
 def test_cfg5_training_step_matches_reference(golden):
-    """The 4-layer stack at B = 2: loss, sampled outputs and every parameter gradient against the
-    reference's (fp32: rtol 1e-3 on gradients that are sums of ~6e6 terms, atol scaled)."""
+    """The 4-layer stack at B = 2: loss, sampled outputs and every parameter gradient against the reference's.
+    Parameter gradients are sums of up to 6.4 million terms: rtol 1e-4 with atol 1e-4 of the largest entry (measured:
+    1e-5 of the largest entry or less). One exception, stated with its cause: the weight gradient of layer 3 (erosion,
+    MAX merge) routes every output gradient to ONE winning tap and channel; where two candidates lie closer than the
+    float rounding of layer 2's smorph output (itself only equal to the reference's within rtol 1e-4) the winner
+    flips and a whole gradient moves to another bin. Measured worst deviation 8.7e-4 of the largest entry, the same
+    on every run; that layer is held to 2e-3 of the largest entry."""
     data = golden("full_size")
     model = build_cfg5()
     x, target = WL.cfg5_batch(B=256, start=0, count=2)
     out = model(x.cuda())
     loss = torch.nn.functional.mse_loss(out, target.cuda())
     loss.backward()
-    assert abs(loss.item() - data["cfg5_loss"][0]) < 1e-4 * abs(data["cfg5_loss"][0])
+    assert abs(loss.item() - data["cfg5_loss"][0]) < 1e-5 * abs(data["cfg5_loss"][0])
     pos = torch.from_numpy(data["cfg5_out_pos"]).cuda()
     np.testing.assert_allclose(out.detach().reshape(-1)[pos].cpu().numpy(), data["cfg5_out_val"], rtol=1e-4, atol=1e-4)
     for n, layer in enumerate(model):
         want = data[f"cfg5_gw{n}"]
-        np.testing.assert_allclose(layer.weight.grad.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * float(np.abs(want).max()))
+        scale = float(np.abs(want).max())
+        tol = dict(rtol=1e-4, atol=2e-3 * scale) if n == 2 else dict(rtol=1e-4, atol=1e-4 * scale)
+        np.testing.assert_allclose(layer.weight.grad.cpu().numpy(), want, **tol, err_msg=f"grad_weight of layer {n}")
         if hasattr(layer, "alpha"):
             want = data[f"cfg5_galpha{n}"]
-            np.testing.assert_allclose(layer.alpha.grad.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * float(np.abs(want).max()))
+            np.testing.assert_allclose(layer.alpha.grad.cpu().numpy(), want, rtol=1e-4, atol=1e-4 * float(np.abs(want).max()),
+                                       err_msg=f"grad_alpha of layer {n}")
 
 
 def test_compositions(F):

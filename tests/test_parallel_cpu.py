@@ -1,8 +1,12 @@
 """Data-parallel plumbing on CPU: world_size-2 gloo ranks (no GPU). The flat gradient bucket must give
-every rank the mean of the per-rank gradients, shards must tile the batch, and a rank whose bucket
-differs must be reported on the host instead of hanging a collective."""
+every rank the mean of the per-rank gradients, shards must tile the batch, a rank whose bucket
+differs must be reported on the host instead of hanging a collective, a rank that leaves between two
+steps must end its peer's next all-reduce with an error instead of a hang, and a gradient that no
+longer aliases the bucket must be refused."""
+import datetime
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -25,7 +29,7 @@ def worker(rank, world, port, mode, results):
     spec.loader.exec_module(par)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8 if mode == "leaver" else 120))
     try:
         torch.manual_seed(0)
         extra = 1 if (mode == "mismatch" and rank == 1) else 0
@@ -38,19 +42,50 @@ def worker(rank, world, port, mode, results):
         loss = sum((data[b] * p).pow(2).sum() for b in range(start, start + count) for p in params) / count
         loss.backward()
         assert params[0].grad.data_ptr() == bucket.flat.data_ptr(), "gradients must accumulate inside the flat bucket"
+        if mode == "rebound":
+            for p in params:
+                p.grad = None               # what optimizer.zero_grad() does by default
+            params[0].grad = torch.ones_like(params[0])
         try:
             bucket.all_reduce(average=True)
             results[rank] = ("ok", bucket.flat.clone())
         except RuntimeError as err:
             results[rank] = ("error", str(err))
+        if mode == "leaver":
+            # Step 1 is done on both ranks. Rank 1 leaves between the steps, with no collective in flight; rank 0 starts
+            # step 2 and must come back with an error within the group's time-out instead of waiting for ever.
+            if rank == 1:
+                os._exit(0)
+            started = time.monotonic()
+            try:
+                bucket.all_reduce(average=True)
+                results["step2"] = ("ok", time.monotonic() - started)
+            except Exception as err:  # gloo reports a lost peer as RuntimeError or DistBackendError
+                results["step2"] = ("error", time.monotonic() - started, type(err).__name__)
+            os._exit(0)                     # the process group cannot be torn down cleanly without its peer
     finally:
-        dist.destroy_process_group()
+        if mode != "leaver":
+            dist.destroy_process_group()
 
 
 def run(mode):
     world = 2
     manager = mp.Manager()
     results = manager.dict()
+    if mode == "leaver":
+        # the ranks end with os._exit: join them by hand instead of through mp.spawn's error handling
+        ctx = mp.get_context("spawn")
+        port = free_port()
+        procs = [ctx.Process(target=worker, args=(r, world, port, mode, results)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            if p.is_alive():
+                p.kill()
+                p.join()
+                results["step2"] = ("hang", 120.0)
+        return dict(results)
     mp.spawn(worker, args=(world, free_port(), mode, results), nprocs=world, join=True)
     return dict(results)
 
@@ -83,6 +118,20 @@ def test_bucket_all_reduce_gives_the_global_mean_gradient():
     loss.backward()
     want = torch.cat([p.grad.reshape(-1) for p in params])
     torch.testing.assert_close(results[0][1], want, rtol=1e-6, atol=1e-6)
+
+
+def test_rebound_gradients_are_refused():
+    results = run("rebound")
+    for rank in (0, 1):
+        assert results[rank][0] == "error" and "no longer a view of the flat buffer" in results[rank][1]
+
+
+def test_rank_leaving_between_steps_ends_the_next_all_reduce_with_an_error():
+    results = run("leaver")
+    assert results[0][0] == "ok", "step 1 ran with both ranks present"
+    outcome = results["step2"]
+    assert outcome[0] == "error", f"the all-reduce without its peer returned {outcome}"
+    assert outcome[1] < 60, f"took {outcome[1]:.1f} s: that is a hang, not a time-out"
 
 
 def test_mismatched_buckets_are_reported_not_hung():
