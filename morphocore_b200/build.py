@@ -32,6 +32,19 @@ def _headers():
     return [inc] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
 
 
+def _includes(path, seen=None):
+    """Files a source reaches through #include "..." (transitively): what its object depends on."""
+    import re
+    seen = set() if seen is None else seen
+    if path in seen or not os.path.exists(path):
+        return seen
+    seen.add(path)
+    with open(path) as f:
+        for name in re.findall(r'^\s*#\s*include\s+"([^"]+)"', f.read(), flags=re.M):
+            _includes(os.path.normpath(os.path.join(os.path.dirname(path), name)), seen)
+    return seen
+
+
 def build_cuda(force=False, verbose=False):
     os.makedirs(BUILD, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
@@ -40,7 +53,7 @@ def build_cuda(force=False, verbose=False):
 
     def compile_unit(unit):
         src, obj = os.path.join(CSRC, unit), os.path.join(BUILD, unit + ".o")
-        if not force and _newer(obj, [src] + headers):
+        if not force and _newer(obj, sorted(_includes(src))):
             return obj
         cmd = [nvcc, "-c", src, "-o", obj] + NVCC_FLAGS
         proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,6 +1,6 @@
 // Backward dilation / erosion kernels.
 //
-// MAX / MIN merges: one scatter per output pixel from the packed winner index (the reference's
+// MAX / MIN merges: one scatter per output pixel from the packed winner index (replaces the reference's
 // morpho_backward_indices_kernel, morphocore/functional/csrc/cuda/morpho_op_kernels.cuh:609-676).
 // ADD / AVERAGE / IDENTITY merges: every (output, input) channel pair routes the gradient of each pixel
 // to its own extremal tap, recomputed here with a tracked strict comparison in the reference's tap order
@@ -8,6 +8,8 @@
 // csrc/cpp/morpho_op_cpu_backward.hxx:94-156). A winning tap that read padding adds to grad_weight but not
 // to grad_input (csrc/cpp/morpho_op_cpu_backward.hxx:39-41).
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 #include "morpho_forward.cuh"
 
@@ -27,53 +29,113 @@ inline int bin_copies(size_t bins, size_t elem_bytes, size_t budget)
 }
 
 template <typename T>
-struct IndexBackwardArgs
+struct ScatterBackwardArgs
 {
     Geometry g;
     const int32_t* idx;
     const T* gy;
     T* gx;
     T* gw;
-    int pixels_per_block;
-    int copies;  // interleaved copies of the shared weight-gradient bins, 0 = global atomics
-    T sign;      // +1 dilation, -1 erosion
+    int64_t strip;    // pixels of one plane a CTA covers (a multiple of 4 * THREADS)
+    int strips;       // CTAs per plane
+    int copies;       // interleaved copies of the shared weight-gradient bins (a power of two), 0 = global atomics
+    bool vec;         // planes are whole 128-bit vectors and the pointers are aligned: four pixels per load
+    T sign;           // +1 dilation, -1 erosion
 };
 
-/// grid (segments, Co): a CTA owns one output channel, a range of pixels and every batch element, so its
-/// Ci * taps weight-gradient bins stay in shared memory until one flush.
-template <typename T>
-__global__ void __launch_bounds__(THREADS) morpho_backward_index_kernel(const IndexBackwardArgs<T> a)
+/// Backward of the MAX / MIN merges from the packed winners, (channel << 16) | tap: every output pixel sends its
+/// gradient to ONE input pixel and ONE weight bin. HBM-bound work (gy and idx read once, grad_input touched once per
+/// output pixel), so the kernel is shaped for memory parallelism:
+///   - one CTA per (batch element, output channel, strip of the plane): B * Co * strips CTAs, every SM busy whatever
+///     the batch; its Ci * taps weight bins live in shared memory until one flush;
+///   - a thread takes four consecutive pixels per step with 128-bit loads of gy and idx, two steps in flight;
+///   - the four pixels share one row, so the pixel's (h, w) costs one division per step, and K is a compile-time
+///     constant for the specialised widths, so the tap's (kh, kw) costs none.
+/// A winning tap that read padding adds to grad_weight but not to grad_input, as in the reference
+/// (morphocore/functional/csrc/cpp/morpho_op_cpu_backward.hxx:39-41, 78-84).
+template <typename T, int KW>
+__global__ void __launch_bounds__(THREADS) morpho_backward_scatter_kernel(const ScatterBackwardArgs<T> a)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* bins = reinterpret_cast<T*>(smem_raw);
     const Geometry& g = a.g;
-    const int o = blockIdx.y;
+    const int kW = KW > 0 ? KW : g.kW;
     const int taps = g.taps();
     const int nbins = g.Ci * taps;
     const int64_t plane = g.plane();
+    const int strip_id = blockIdx.x % a.strips;
+    const int64_t bo = blockIdx.x / a.strips;          // b * Co + o
+    const int o = static_cast<int>(bo % g.Co);
     const int lane_copy = a.copies > 0 ? (threadIdx.x & (a.copies - 1)) : 0;
 
     for (int e = threadIdx.x; e < nbins * a.copies; e += THREADS) bins[e] = T(0);
     __syncthreads();
 
-    const int64_t p_begin = static_cast<int64_t>(blockIdx.x) * a.pixels_per_block;
-    const int64_t p_end = min(p_begin + a.pixels_per_block, plane);
-    for (int b = 0; b < g.B; b++)
+    const T* gyp = a.gy + bo * plane;
+    const int32_t* ip = a.idx + bo * plane;
+    T* gxb = a.gx + (bo / g.Co) * g.Ci * plane;
+    T* gwo = a.gw + static_cast<int64_t>(o) * nbins;
+    const int64_t p_begin = strip_id * a.strip, p_end = min(p_begin + a.strip, plane);
+
+    auto route = [&](T grad, int32_t packed, int h, int w) {
+        if (grad == T(0)) return;
+        const int ch = packed >> 16, k = packed & 0xFFFF;
+        if (ch < 0 || ch >= g.Ci || k >= taps) return;   // a corrupt index is dropped, never dereferenced
+        const int kh = k / kW, kw = k - kh * kW;
+        const int ih = h + g.pH - kh, iw = w + g.pW - kw;
+        if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) atomic_add(gxb + ch * plane + static_cast<int64_t>(ih) * g.W + iw, grad);
+        if (a.copies > 0) atomic_add(bins + (ch * taps + k) * a.copies + lane_copy, grad);
+        else atomic_add(gwo + ch * taps + k, a.sign * grad);
+    };
+
+    if (a.vec)
     {
-        const int64_t base = (static_cast<int64_t>(b) * g.Co + o) * plane;
-        T* gxb = a.gx + static_cast<int64_t>(b) * g.Ci * plane;
+        constexpr int STEP = 4 * THREADS;
+        auto load = [&](int64_t p, T (&gv)[4], int4& iv) {
+            if (p < p_end)
+            {
+                if constexpr (sizeof(T) == 4)
+                {
+                    const float4 q = __ldg(reinterpret_cast<const float4*>(gyp + p));
+                    gv[0] = q.x; gv[1] = q.y; gv[2] = q.z; gv[3] = q.w;
+                }
+                else
+                {
+                    const double2 q0 = __ldg(reinterpret_cast<const double2*>(gyp + p)), q1 = __ldg(reinterpret_cast<const double2*>(gyp + p + 2));
+                    gv[0] = q0.x; gv[1] = q0.y; gv[2] = q1.x; gv[3] = q1.y;
+                }
+                iv = __ldg(reinterpret_cast<const int4*>(ip + p));
+            }
+            else
+            {
+                gv[0] = gv[1] = gv[2] = gv[3] = T(0);
+                iv = make_int4(0, 0, 0, 0);
+            }
+        };
+        for (int64_t p = p_begin + 4 * threadIdx.x; p < p_end; p += 2 * STEP)
+        {
+            T g0[4], g1[4];
+            int4 i0, i1;
+            load(p, g0, i0);
+            load(p + STEP, g1, i1);
+            {
+                const int h = static_cast<int>(p / g.W), w = static_cast<int>(p - static_cast<int64_t>(h) * g.W);
+                route(g0[0], i0.x, h, w); route(g0[1], i0.y, h, w + 1); route(g0[2], i0.z, h, w + 2); route(g0[3], i0.w, h, w + 3);
+            }
+            if (p + STEP < p_end)
+            {
+                const int64_t q = p + STEP;
+                const int h = static_cast<int>(q / g.W), w = static_cast<int>(q - static_cast<int64_t>(h) * g.W);
+                route(g1[0], i1.x, h, w); route(g1[1], i1.y, h, w + 1); route(g1[2], i1.z, h, w + 2); route(g1[3], i1.w, h, w + 3);
+            }
+        }
+    }
+    else
+    {
         for (int64_t p = p_begin + threadIdx.x; p < p_end; p += THREADS)
         {
-            const T grad = __ldg(a.gy + base + p);
-            if (grad == T(0)) continue;
-            const int32_t packed = __ldg(a.idx + base + p);
-            const int ch = packed >> 16, k = packed & 0xFFFF;
-            if (ch < 0 || ch >= g.Ci || k >= taps) continue;  // never index out of bounds on a corrupt index
-            const int h = static_cast<int>(p / g.W), w = static_cast<int>(p % g.W);
-            const int ih = h + g.pH - k / g.kW, iw = w + g.pW - k % g.kW;
-            if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) atomic_add(gxb + ch * plane + static_cast<int64_t>(ih) * g.W + iw, grad);
-            if (a.copies > 0) atomic_add(bins + (ch * taps + k) * a.copies + lane_copy, grad);
-            else atomic_add(a.gw + static_cast<int64_t>(o) * nbins + ch * taps + k, a.sign * grad);
+            const int h = static_cast<int>(p / g.W);
+            route(__ldg(gyp + p), __ldg(ip + p), h, static_cast<int>(p - static_cast<int64_t>(h) * g.W));
         }
     }
     if (a.copies == 0) return;
@@ -82,36 +144,38 @@ __global__ void __launch_bounds__(THREADS) morpho_backward_index_kernel(const In
     {
         T sum = T(0);
         for (int c = 0; c < a.copies; c++) sum += bins[e * a.copies + c];
-        if (sum != T(0)) atomic_add(a.gw + static_cast<int64_t>(o) * nbins + e, a.sign * sum);
+        if (sum != T(0)) atomic_add(gwo + e, a.sign * sum);
     }
 }
 
-template <typename T>
-int launch_backward_index(const mc_desc& d, const int32_t* idx, const T* gy, T* gx, T* gw, cudaStream_t stream)
+template <typename T, int KW>
+int launch_backward_scatter(const mc_desc& d, const int32_t* idx, const T* gy, T* gx, T* gw, cudaStream_t stream)
 {
-    IndexBackwardArgs<T> a;
+    ScatterBackwardArgs<T> a;
     a.g = make_geometry(d, sizeof(T));
     a.idx = idx; a.gy = gy; a.gx = gx; a.gw = gw;
     a.sign = d.op == MC_OP_DILATION ? T(1) : T(-1);
     const size_t nbins = static_cast<size_t>(d.Ci) * d.kH * d.kW;
-    a.copies = bin_copies(nbins, sizeof(T), 64 * 1024);
+    a.copies = bin_copies(nbins, sizeof(T), 48 * 1024);
     const size_t smem = nbins * a.copies * sizeof(T);
     const int64_t plane = a.g.plane();
-    int64_t segments = (4 * 148 + d.Co - 1) / d.Co;
-    segments = std::min<int64_t>(segments, (plane + THREADS - 1) / THREADS);
-    segments = std::max<int64_t>(segments, (plane + 0x3fffffff) / 0x40000000);
-    segments = std::max<int64_t>(segments, 1);
-    a.pixels_per_block = static_cast<int>((plane + segments - 1) / segments);
-    if (d.Co > 65535)
-    {
-        set_last_error("more than 65535 output channels");
-        return MC_ERR_UNSUPPORTED;
-    }
-    auto kernel = morpho_backward_index_kernel<T>;
+    a.vec = d.W % 4 == 0 && reinterpret_cast<uintptr_t>(gy) % 16 == 0 && reinterpret_cast<uintptr_t>(idx) % 16 == 0;
+    // Enough CTAs to fill the device several times over, but strips long enough that the flush of the bins
+    // (Ci * taps global atomics per CTA) stays small beside the strip's own scatter.
+    constexpr int64_t QUANTUM = 4 * THREADS;
+    const int64_t pairs = static_cast<int64_t>(d.B) * d.Co;
+    int64_t strips = (148 * 8 + pairs - 1) / pairs;
+    const int64_t min_strip = std::max<int64_t>(QUANTUM, (static_cast<int64_t>(nbins) * 8 + QUANTUM - 1) / QUANTUM * QUANTUM);
+    strips = std::min<int64_t>(strips, (plane + min_strip - 1) / min_strip);
+    strips = std::max<int64_t>(strips, 1);
+    a.strip = ((plane + strips - 1) / strips + QUANTUM - 1) / QUANTUM * QUANTUM;
+    a.strips = static_cast<int>((plane + a.strip - 1) / a.strip);
+    const int64_t blocks = pairs * a.strips;
+    if (blocks > 0x7fffffffLL) { set_last_error("too many strips for one launch"); return MC_ERR_UNSUPPORTED; }
+    auto kernel = morpho_backward_scatter_kernel<T, KW>;
     if (!allow_shared(kernel, smem)) { set_last_error("cannot opt in to %zu bytes of shared memory", smem); return MC_ERR_UNSUPPORTED; }
-    const dim3 grid(static_cast<unsigned>((plane + a.pixels_per_block - 1) / a.pixels_per_block), static_cast<unsigned>(d.Co));
-    kernel<<<grid, THREADS, smem, stream>>>(a);
-    return check_launch("morpho_backward_index_kernel");
+    kernel<<<static_cast<unsigned>(blocks), THREADS, smem, stream>>>(a);
+    return check_launch("morpho_backward_scatter_kernel");
 }
 
 template <typename T>
@@ -322,9 +386,146 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
     }
 }
 
+/// Backward of the IDENTITY merge for the specialised square widths (any dtype): each channel is paired with itself,
+/// so a CTA owns ONE (batch element, channel, tile) pair and every output pixel emits exactly one gradient.
+/// Replaces the reference's morpho_backward_pairs_kernel for this case
+/// (morphocore/functional/csrc/cuda/morpho_op_kernels.cuh:479-602) with a shape of its own:
+///   - the extremum pass is the forward kernel's inner loop (add, compare, select per tap: nothing is tracked per
+///     tap); per kernel ROW the row extremum is compared once with the running best and the first improving row
+///     is kept (rows ascend, so ties go to the lower kh);
+///   - a second pass scans that one row, from the last column down, for the lowest kw whose candidate equals the
+///     best: together the first tap in kh-major, kw order that attains the extremum, the reference's winner
+///     (csrc/cpp/morpho_op_cpu_kernels.hxx:212-252); index 0 when nothing beats the initial value;
+///   - grad_input: one global atomic per output pixel straight to its target (no shared gradient window to zero,
+///     fill and flush: with one pair per CTA it would be traversed for 2048 contributions);
+///   - grad_weight: interleaved shared bins, flushed once per CTA.
+template <typename T, bool IS_MIN, int KW>
+__global__ void __launch_bounds__(THREADS, 2) morpho_backward_identity_kernel(const PairsBackwardArgs<T> a)
+{
+    static_assert(KW > 0, "specialised widths only");
+    constexpr int TAPS = KW * KW;
+    constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T)), STRIDE = window_stride(KW, sizeof(T));
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const Geometry& g = a.g;
+    T* sx = reinterpret_cast<T*>(smem_raw);
+    T* sw = sx + g.window_elems();               // [KW][KW], negated for erosion
+    T* bins = sw + (TAPS + 3) / 4 * 4;           // [TAPS][copies]
+
+    const int tiles = g.tiles_x * g.tiles_y;
+    const int ci = blockIdx.x % g.Ci;
+    const int tile = (blockIdx.x / g.Ci) % tiles;
+    const int b = blockIdx.x / (g.Ci * tiles);
+    const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
+    int tx, ty;
+    bool warp_live;
+    thread_patch(tile_h0, tile_w0, g.H, g.W, tx, ty, warp_live);
+    const int64_t plane = g.plane();
+    const int lane_copy = threadIdx.x & (a.copies - 1);
+    const T op_init = IS_MIN ? Limits<T>::inf() : -Limits<T>::inf();
+    const int h0 = tile_h0 + ty * PATCH_H, w0 = tile_w0 + tx * PATCH_W;
+
+    // The thread's eight output gradients first: their latency hides behind the staging of the window.
+    T grad[PATCH_H][PATCH_W];
+    bool any = false;
+#pragma unroll
+    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            T v = T(0);
+            if (h0 + rr < g.H && w0 + j < g.W) v = __ldg(a.gy + ((static_cast<int64_t>(b) * g.Co + ci) * g.H + h0 + rr) * g.W + w0 + j) * a.scale;
+            grad[rr][j] = v;
+            any |= v != T(0);
+        }
+
+    load_window(sx, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0, tile_w0, a.fill);
+    {
+        const T* wb = a.w + static_cast<int64_t>(b) * g.weight_batch_stride + static_cast<int64_t>(ci) * TAPS;
+        for (int e = threadIdx.x; e < TAPS; e += THREADS)
+        {
+            const T v = __ldg(wb + e);
+            sw[e] = IS_MIN ? -v : v;
+        }
+    }
+    for (int e = threadIdx.x; e < TAPS * a.copies; e += THREADS) bins[e] = T(0);
+    __syncthreads();
+
+    if (warp_live && __any_sync(0xffffffffu, any))
+    {
+        const T* base = sx + (ty * PATCH_H) * STRIDE + tx * PATCH_W;
+        T best[PATCH_H][PATCH_W];
+        int row[PATCH_H][PATCH_W];
+#pragma unroll
+        for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+            for (int j = 0; j < PATCH_W; j++)
+            {
+                best[rr][j] = op_init;
+                row[rr][j] = 0;
+            }
+#pragma unroll(KW <= 7 ? KW : 1)
+        for (int kh = 0; kh < KW; kh++)
+        {
+            T seg[PATCH_H][LEN];
+#pragma unroll
+            for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], base + (rr + KW - 1 - kh) * STRIDE);
+            T wv[KW];
+#pragma unroll
+            for (int kw = 0; kw < KW; kw++) wv[kw] = sw[kh * KW + kw];
+#pragma unroll
+            for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                for (int j = 0; j < PATCH_W; j++)
+                {
+                    T rb = op_init;
+#pragma unroll
+                    for (int kw = 0; kw < KW; kw++) rb = ext2<IS_MIN>(rb, seg[rr][OFF + j + KW - 1 - kw] + wv[kw]);
+                    if (strictly_better<IS_MIN>(rb, best[rr][j]))
+                    {
+                        best[rr][j] = rb;
+                        row[rr][j] = kh;
+                    }
+                }
+        }
+
+        T* gxp = a.gx + (static_cast<int64_t>(b) * g.Ci + ci) * plane;
+#pragma unroll
+        for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+            for (int j = 0; j < PATCH_W; j++)
+            {
+                const T v = grad[rr][j];
+                if (v == T(0)) continue;
+                int kh = 0, kw = 0;
+                const T target = best[rr][j];
+                if (target != op_init)    // something beat the initial value (never true for NaN)
+                {
+                    kh = row[rr][j];
+                    kw = KW - 1;
+                    const T* xr = base + (rr + KW - 1 - kh) * STRIDE + OFF + j;
+                    const T* wr = sw + kh * KW;
+#pragma unroll
+                    for (int q = KW - 2; q >= 0; q--)
+                        if (xr[KW - 1 - q] + wr[q] == target) kw = q;
+                }
+                const int ih = h0 + rr + g.pH - kh, iw = w0 + j + g.pW - kw;
+                if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) atomic_add(gxp + static_cast<int64_t>(ih) * g.W + iw, v);
+                atomic_add(bins + (kh * KW + kw) * a.copies + lane_copy, v);
+            }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < TAPS; e += THREADS)
+    {
+        T sum = T(0);
+        for (int c = 0; c < a.copies; c++) sum += bins[e * a.copies + c];
+        if (sum != T(0)) atomic_add(a.gw + static_cast<int64_t>(ci) * TAPS + e, a.sign * sum);
+    }
+}
+
 }  // namespace mc
 
 #include "morpho_backward_rows.cuh"
+#include "morpho_backward_regs.cuh"
 
 namespace mc
 {
@@ -341,6 +542,19 @@ int launch_backward_pairs(const mc_desc& d, const T* x, const T* w, const T* gy,
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
     const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * d.Ci * d.B;
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
+    if constexpr (sizeof(T) == 4 && (KW == 3 || KW == 5))
+    {
+        const size_t bytes = pairs_regs_smem<KW>(a.g, a.g.identity ? 1 : d.Co);
+        if (bytes > 0)
+        {
+            auto fast = morpho_backward_pairs_regs_kernel<IS_MIN, KW>;
+            if (allow_shared(fast, bytes))
+            {
+                fast<<<static_cast<unsigned>(blocks), THREADS, bytes, stream>>>(a);
+                return check_launch("morpho_backward_pairs_regs_kernel");
+            }
+        }
+    }
     if constexpr (sizeof(T) == 4 && (KW == 3 || KW == 5 || KW == 7))
     {
         const size_t bytes = pairs_rows_smem<KW>(a.g, a.g.identity ? 1 : d.Co);
@@ -351,6 +565,20 @@ int launch_backward_pairs(const mc_desc& d, const T* x, const T* w, const T* gy,
             {
                 fast<<<static_cast<unsigned>(blocks), THREADS, bytes, stream>>>(a);
                 return check_launch("morpho_backward_pairs_rows_kernel");
+            }
+        }
+    }
+    if constexpr (KW > 0)
+    {
+        if (a.g.identity)
+        {
+            a.copies = bin_copies(taps, sizeof(T), 8 * 1024);
+            const size_t bytes = (static_cast<size_t>(a.g.window_elems()) + (taps + 3) / 4 * 4 + taps * a.copies) * sizeof(T);
+            auto kernel = morpho_backward_identity_kernel<T, IS_MIN, KW>;
+            if (a.copies >= 1 && bytes <= MAX_SHARED_BYTES && allow_shared(kernel, bytes))
+            {
+                kernel<<<static_cast<unsigned>(blocks), THREADS, bytes, stream>>>(a);
+                return check_launch("morpho_backward_identity_kernel");
             }
         }
     }

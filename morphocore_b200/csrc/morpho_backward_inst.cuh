@@ -15,7 +15,7 @@ int morpho_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const 
     constexpr int WIDE = sizeof(T) == 4 ? 4 : 2;
     const size_t taps = static_cast<size_t>(d.kH) * d.kW;
     const size_t wnumel = static_cast<size_t>(d.Co) * (d.merge == MC_MERGE_IDENTITY ? 1 : d.Ci) * taps;
-    // The kernels accumulate into the gradients.
+    // Both gradients are sums that the kernels below build up with atomic adds: start from zero.
     if (cudaMemsetAsync(gx, 0, sizeof(T) * static_cast<size_t>(d.B) * d.Ci * d.H * d.W, stream) != cudaSuccess
         || cudaMemsetAsync(gw, 0, sizeof(T) * wnumel, stream) != cudaSuccess)
     {
@@ -31,7 +31,7 @@ int morpho_backward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const 
             if (rc != MC_OK) return rc;
             idx = static_cast<const int32_t*>(ws);
         }
-        return launch_backward_index<T>(d, idx, gy, gx, gw, stream);
+        return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) { return launch_backward_scatter<T, decltype(kw)::value>(d, idx, gy, gx, gw, stream); });
     }
     const int ob = output_block<T>(d);
     return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
