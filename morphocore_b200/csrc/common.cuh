@@ -167,6 +167,47 @@ __device__ __forceinline__ void load_window(T* __restrict__ dst, const T* __rest
     }
 }
 
+/// Asynchronous copy of one element from global to shared memory (cp.async: no register staging, completion awaited
+/// with cp_async_wait_all). 4 or 8 bytes.
+template <typename T>
+__device__ __forceinline__ void cp_async_element(T* dst, const T* src)
+{
+    static_assert(sizeof(T) == 4 || sizeof(T) == 8, "float or double");
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+    if constexpr (sizeof(T) == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+/// load_window with every copy of a thread in flight at once: in-image (or clamped, for REPLICATE) elements travel by
+/// cp.async straight into shared memory, out-of-image ones are stored as `outside`. The window's row stride is the
+/// compile-time STRIDE and `at(c)` maps a column to its element offset inside the stored row (identity, or a swizzle).
+/// The caller runs cp_async_wait_all() and a CTA barrier before reading the window.
+template <int STRIDE, typename T, typename At>
+__device__ __forceinline__ void stage_window_async(T* __restrict__ dst, const T* __restrict__ plane, const Geometry& g, int tile_h0, int tile_w0,
+                                                   T outside, At at)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - g.halo_left();
+    // Warps take rows, lanes take columns: no division, one clamped row pointer per row.
+    for (int r = warp; r < g.win_rows; r += THREADS / 32)
+    {
+        const int iy = row0 + r;
+        const bool row_in = iy >= 0 && iy < g.H;
+        const T* src = plane + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W;
+        T* out = dst + r * STRIDE;
+#pragma unroll
+        for (int m = 0; m < (STRIDE + 31) / 32; m++)
+        {
+            const int c = lane + 32 * m;
+            if (c >= STRIDE) break;
+            const int ix = col0 + c;
+            if ((row_in && ix >= 0 && ix < g.W) || g.replicate) cp_async_element(out + at(c), src + min(max(ix, 0), g.W - 1));
+            else out[at(c)] = outside;
+        }
+    }
+}
+
 /// Stage the window of one plane for the smorph kernels, whose taps outside the image are excluded. Both
 /// windows hold x inside the image; outside, `low` (read by pairs with alpha >= 0, u = x + w) holds -big and
 /// `high` (read by pairs with alpha < 0, u = -x - w) holds +big, so that u = -big there: a value that never

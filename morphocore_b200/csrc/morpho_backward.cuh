@@ -191,6 +191,7 @@ struct PairsBackwardArgs
     T scale;   // 1 / Ci for AVERAGE
     T sign;    // +1 dilation, -1 erosion
     int copies;
+    int channels_per_cta;   // identity kernel: channels of one tile a CTA walks
 };
 
 /// A CTA owns (batch element, input channel, tile): it stages the input window once, loops over the
@@ -386,35 +387,63 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_kernel(const
     }
 }
 
+/// Column of a window row -> element offset inside the stored row. With SWIZZLE the 16-byte vectors (two doubles) of a
+/// row are permuted: vector n is stored at n ^ ((n >> 3) & 1), i.e. the two vectors of every other 32-byte pair swap
+/// places. Lanes 0..7 of a quarter warp read vectors 2 tx + i; after the swap lanes 0..3 and lanes 4..7 land in bank
+/// groups of different parity, so the eight lanes cover all eight bank groups and the load is conflict free.
+template <bool SWIZZLE> struct SwizzledRow
+{
+    __device__ __forceinline__ static int at(int c)
+    {
+        if constexpr (SWIZZLE) return c ^ ((c >> 3) & 2);   // doubles: vector index c >> 1, its bit 3 is bit 4 of c; flip bit 1 of c
+        else return c;
+    }
+};
+
+/// Channels of one tile a CTA of the identity kernel walks. The kernel can pipeline several (the window of the next
+/// channel is copied while the current one computes), but on B200 one channel per CTA measured fastest on the fp64
+/// 11 x 11 case (5.35 ms against 5.7 - 5.9 ms for 2, 4 and 8): two co-resident CTAs already overlap each other's
+/// staging, and more CTAs balance the SMs better.
+constexpr int IDENTITY_CHANNELS_PER_CTA = 1;
+
 /// Backward of the IDENTITY merge for the specialised square widths (any dtype): each channel is paired with itself,
-/// so a CTA owns ONE (batch element, channel, tile) pair and every output pixel emits exactly one gradient.
+/// so a (batch element, channel, tile) triple is one pair and every output pixel emits exactly one gradient.
 /// Replaces the reference's morpho_backward_pairs_kernel for this case
 /// (morphocore/functional/csrc/cuda/morpho_op_kernels.cuh:479-602) with a shape of its own:
+///   - the window and the structuring element travel into shared memory by cp.async, every copy of a thread in flight
+///     at once; a CTA may walk several channels of its tile (IDENTITY_CHANNELS_PER_CTA), the next channel's copies
+///     landing in the other of two buffers while the current channel computes;
 ///   - the extremum pass is the forward kernel's inner loop (add, compare, select per tap: nothing is tracked per
 ///     tap); per kernel ROW the row extremum is compared once with the running best and the first improving row
-///     is kept (rows ascend, so ties go to the lower kh);
+///     is kept (rows ascend, so ties go to the lower kh); every window row is loaded into registers once and serves
+///     both patch rows;
 ///   - a second pass scans that one row, from the last column down, for the lowest kw whose candidate equals the
 ///     best: together the first tap in kh-major, kw order that attains the extremum, the reference's winner
 ///     (csrc/cpp/morpho_op_cpu_kernels.hxx:212-252); index 0 when nothing beats the initial value;
 ///   - grad_input: one global atomic per output pixel straight to its target (no shared gradient window to zero,
-///     fill and flush: with one pair per CTA it would be traversed for 2048 contributions);
-///   - grad_weight: interleaved shared bins, flushed once per CTA.
+///     fill and flush: with one pair it would be traversed for 2048 contributions);
+///   - grad_weight: interleaved shared bins, flushed after each channel.
 template <typename T, bool IS_MIN, int KW>
 __global__ void __launch_bounds__(THREADS, 2) morpho_backward_identity_kernel(const PairsBackwardArgs<T> a)
 {
     static_assert(KW > 0, "specialised widths only");
-    constexpr int TAPS = KW * KW;
+    constexpr int TAPS = KW * KW, TAPS_PAD = (TAPS + 3) / 4 * 4;
     constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T)), STRIDE = window_stride(KW, sizeof(T));
+    constexpr int PER = 16 / sizeof(T), VECS = LEN / PER;
+    constexpr int WINDOW = (TILE_H + KW - 1) * STRIDE;
+    using Row = SwizzledRow<sizeof(T) == 8>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const Geometry& g = a.g;
-    T* sx = reinterpret_cast<T*>(smem_raw);
-    T* sw = sx + g.window_elems();               // [KW][KW], negated for erosion
-    T* bins = sw + (TAPS + 3) / 4 * 4;           // [TAPS][copies]
+    T* sx0 = reinterpret_cast<T*>(smem_raw);     // two windows
+    T* sw0 = sx0 + 2 * WINDOW;                   // two structuring elements [KW][KW]
+    T* bins = sw0 + 2 * TAPS_PAD;                // [TAPS][copies]
 
     const int tiles = g.tiles_x * g.tiles_y;
-    const int ci = blockIdx.x % g.Ci;
-    const int tile = (blockIdx.x / g.Ci) % tiles;
-    const int b = blockIdx.x / (g.Ci * tiles);
+    const int groups = (g.Ci + a.channels_per_cta - 1) / a.channels_per_cta;
+    const int c_begin = (blockIdx.x % groups) * a.channels_per_cta;
+    const int c_count = min(a.channels_per_cta, g.Ci - c_begin);
+    const int tile = (blockIdx.x / groups) % tiles;
+    const int b = blockIdx.x / (groups * tiles);
     const int tile_h0 = (tile / g.tiles_x) * TILE_H, tile_w0 = (tile % g.tiles_x) * TILE_W;
     int tx, ty;
     bool warp_live;
@@ -422,103 +451,146 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_identity_kernel(co
     const int64_t plane = g.plane();
     const int lane_copy = threadIdx.x & (a.copies - 1);
     const T op_init = IS_MIN ? Limits<T>::inf() : -Limits<T>::inf();
-    const int h0 = tile_h0 + ty * PATCH_H, w0 = tile_w0 + tx * PATCH_W;
+    const int h0 = tile_h0 + ty * PATCH_H, w0 = tile_w0 + tx * PATCH_W, y0 = ty * PATCH_H;
+    const T* wbase = a.w + static_cast<int64_t>(b) * g.weight_batch_stride;
 
-    // The thread's eight output gradients first: their latency hides behind the staging of the window.
-    T grad[PATCH_H][PATCH_W];
-    bool any = false;
+    // Element offsets of the thread's segment vectors inside a (swizzled) window row: constant over rows and channels.
+    int vec_at[VECS];
 #pragma unroll
-    for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-        for (int j = 0; j < PATCH_W; j++)
-        {
-            T v = T(0);
-            if (h0 + rr < g.H && w0 + j < g.W) v = __ldg(a.gy + ((static_cast<int64_t>(b) * g.Co + ci) * g.H + h0 + rr) * g.W + w0 + j) * a.scale;
-            grad[rr][j] = v;
-            any |= v != T(0);
-        }
+    for (int i = 0; i < VECS; i++) vec_at[i] = Row::at(tx * PATCH_W + i * PER);
 
-    load_window(sx, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0, tile_w0, a.fill);
-    {
-        const T* wb = a.w + static_cast<int64_t>(b) * g.weight_batch_stride + static_cast<int64_t>(ci) * TAPS;
-        for (int e = threadIdx.x; e < TAPS; e += THREADS)
-        {
-            const T v = __ldg(wb + e);
-            sw[e] = IS_MIN ? -v : v;
-        }
-    }
+    auto stage = [&](int n) {
+        const int c = c_begin + n;
+        stage_window_async<STRIDE>(sx0 + (n & 1) * WINDOW, a.x + (static_cast<int64_t>(b) * g.Ci + c) * plane, g, tile_h0, tile_w0, a.fill,
+                                   [](int col) { return Row::at(col); });
+        for (int e = threadIdx.x; e < TAPS; e += THREADS) cp_async_element(sw0 + (n & 1) * TAPS_PAD + e, wbase + static_cast<int64_t>(c) * TAPS + e);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
     for (int e = threadIdx.x; e < TAPS * a.copies; e += THREADS) bins[e] = T(0);
-    __syncthreads();
-
-    if (warp_live && __any_sync(0xffffffffu, any))
+    stage(0);
+    for (int n = 0; n < c_count; n++)
     {
-        const T* base = sx + (ty * PATCH_H) * STRIDE + tx * PATCH_W;
-        T best[PATCH_H][PATCH_W];
-        int row[PATCH_H][PATCH_W];
+        const int ci = c_begin + n;
+        const T* sx = sx0 + (n & 1) * WINDOW;
+        const T* sw = sw0 + (n & 1) * TAPS_PAD;   // as stored by the caller: erosion subtracts it below
+
+        // Is any of the thread's eight output gradients non-zero? (They are read again, from cache, when they are
+        // routed: holding them through the extremum pass would cost sixteen registers in double.)
+        const T* gyp = a.gy + ((static_cast<int64_t>(b) * g.Co + ci) * g.H + h0) * g.W + w0;
+        bool any = false;
 #pragma unroll
         for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
             for (int j = 0; j < PATCH_W; j++)
-            {
-                best[rr][j] = op_init;
-                row[rr][j] = 0;
-            }
-#pragma unroll(KW <= 7 ? KW : 1)
-        for (int kh = 0; kh < KW; kh++)
+                if (h0 + rr < g.H && w0 + j < g.W) any |= __ldg(gyp + static_cast<int64_t>(rr) * g.W + j) != T(0);
+        if (n + 1 < c_count)
         {
-            T seg[PATCH_H][LEN];
+            stage(n + 1);   // the other buffer: its last readers passed the barrier that ended channel n - 1
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+
+        if (warp_live && __any_sync(0xffffffffu, any))
+        {
+            auto load_row = [&](T (&seg)[LEN], int window_row) {
+                const T* row = sx + window_row * STRIDE;
 #pragma unroll
-            for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], base + (rr + KW - 1 - kh) * STRIDE);
-            T wv[KW];
-#pragma unroll
-            for (int kw = 0; kw < KW; kw++) wv[kw] = sw[kh * KW + kw];
+                for (int i = 0; i < VECS; i++) lds128(&seg[i * PER], row + vec_at[i]);
+            };
+            T best[PATCH_H][PATCH_W];
+            int row[PATCH_H][PATCH_W];
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
                 for (int j = 0; j < PATCH_W; j++)
                 {
-                    T rb = op_init;
+                    best[rr][j] = op_init;
+                    row[rr][j] = 0;
+                }
+            // Kernel row kh reads window row y + KW-1-kh for the patch row y: the lower patch row's window row at kh is
+            // the upper patch row's at kh + 1, so every window row is loaded once and the two segment buffers swap roles.
+            static_assert(PATCH_H == 2, "two segment buffers, one per patch row");
+            auto row_pass = [&](int kh, const T (&upper)[LEN], const T (&lower)[LEN]) {
+                // Taps outermost: one structuring-element value in registers at a time, eight independent chains.
+                T rb[PATCH_H][PATCH_W];
 #pragma unroll
-                    for (int kw = 0; kw < KW; kw++) rb = ext2<IS_MIN>(rb, seg[rr][OFF + j + KW - 1 - kw] + wv[kw]);
-                    if (strictly_better<IS_MIN>(rb, best[rr][j]))
+                for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                    for (int j = 0; j < PATCH_W; j++) rb[rr][j] = op_init;
+#pragma unroll
+                for (int kw = 0; kw < KW; kw++)
+                {
+                    const T wv = IS_MIN ? -sw[kh * KW + kw] : sw[kh * KW + kw];
+#pragma unroll
+                    for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                        for (int j = 0; j < PATCH_W; j++) rb[rr][j] = ext2<IS_MIN>(rb[rr][j], (rr == 0 ? upper : lower)[OFF + j + KW - 1 - kw] + wv);
+                }
+#pragma unroll
+                for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                    for (int j = 0; j < PATCH_W; j++)
+                        if (strictly_better<IS_MIN>(rb[rr][j], best[rr][j]))
+                        {
+                            best[rr][j] = rb[rr][j];
+                            row[rr][j] = kh;
+                        }
+            };
+            T seg_a[LEN], seg_b[LEN];
+            load_row(seg_b, y0 + KW);   // window row of patch row 1 at kh = 0
+#pragma unroll(KW <= 7 ? (KW + 1) / 2 : 1)
+            for (int kh = 0; kh < KW; kh += 2)
+            {
+                load_row(seg_a, y0 + KW - 1 - kh);
+                row_pass(kh, seg_a, seg_b);
+                if (kh + 1 < KW)
+                {
+                    load_row(seg_b, y0 + KW - 2 - kh);
+                    row_pass(kh + 1, seg_b, seg_a);
+                }
+            }
+
+            T* gxp = a.gx + (static_cast<int64_t>(b) * g.Ci + ci) * plane;
+#pragma unroll
+            for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                for (int j = 0; j < PATCH_W; j++)
+                {
+                    if (h0 + rr >= g.H || w0 + j >= g.W) continue;
+                    const T v = __ldg(gyp + static_cast<int64_t>(rr) * g.W + j) * a.scale;
+                    if (v == T(0)) continue;
+                    int kh = 0, kw = 0;
+                    const T target = best[rr][j];
+                    if (target != op_init)    // something beat the initial value (never true for NaN)
                     {
-                        best[rr][j] = rb;
-                        row[rr][j] = kh;
+                        kh = row[rr][j];
+                        kw = KW - 1;
+                        const T* xr = sx + (y0 + rr + KW - 1 - kh) * STRIDE;
+                        const int c0 = tx * PATCH_W + OFF + j;
+                        const T* wr = sw + kh * KW;
+#pragma unroll
+                        for (int q = KW - 2; q >= 0; q--)
+                            if (xr[Row::at(c0 + KW - 1 - q)] + (IS_MIN ? -wr[q] : wr[q]) == target) kw = q;
                     }
+                    const int ih = h0 + rr + g.pH - kh, iw = w0 + j + g.pW - kw;
+                    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) atomic_add(gxp + static_cast<int64_t>(ih) * g.W + iw, v);
+                    atomic_add(bins + (kh * KW + kw) * a.copies + lane_copy, v);
                 }
         }
-
-        T* gxp = a.gx + (static_cast<int64_t>(b) * g.Ci + ci) * plane;
-#pragma unroll
-        for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-            for (int j = 0; j < PATCH_W; j++)
+        __syncthreads();   // every warp is done with this channel's buffers and bins
+        for (int e = threadIdx.x; e < TAPS; e += THREADS)
+        {
+            T sum = T(0);
+            for (int c = 0; c < a.copies; c++)
             {
-                const T v = grad[rr][j];
-                if (v == T(0)) continue;
-                int kh = 0, kw = 0;
-                const T target = best[rr][j];
-                if (target != op_init)    // something beat the initial value (never true for NaN)
-                {
-                    kh = row[rr][j];
-                    kw = KW - 1;
-                    const T* xr = base + (rr + KW - 1 - kh) * STRIDE + OFF + j;
-                    const T* wr = sw + kh * KW;
-#pragma unroll
-                    for (int q = KW - 2; q >= 0; q--)
-                        if (xr[KW - 1 - q] + wr[q] == target) kw = q;
-                }
-                const int ih = h0 + rr + g.pH - kh, iw = w0 + j + g.pW - kw;
-                if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) atomic_add(gxp + static_cast<int64_t>(ih) * g.W + iw, v);
-                atomic_add(bins + (kh * KW + kw) * a.copies + lane_copy, v);
+                sum += bins[e * a.copies + c];
+                bins[e * a.copies + c] = T(0);
             }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < TAPS; e += THREADS)
-    {
-        T sum = T(0);
-        for (int c = 0; c < a.copies; c++) sum += bins[e * a.copies + c];
-        if (sum != T(0)) atomic_add(a.gw + static_cast<int64_t>(ci) * TAPS + e, a.sign * sum);
+            if (sum != T(0)) atomic_add(a.gw + static_cast<int64_t>(ci) * TAPS + e, a.sign * sum);
+        }
+        // the next channel's first bin update comes after its own barrier above
     }
 }
 
@@ -573,11 +645,14 @@ int launch_backward_pairs(const mc_desc& d, const T* x, const T* w, const T* gy,
         if (a.g.identity)
         {
             a.copies = bin_copies(taps, sizeof(T), 8 * 1024);
-            const size_t bytes = (static_cast<size_t>(a.g.window_elems()) + (taps + 3) / 4 * 4 + taps * a.copies) * sizeof(T);
+            const size_t bytes = (2 * static_cast<size_t>(a.g.window_elems()) + 2 * ((taps + 3) / 4 * 4) + taps * a.copies) * sizeof(T);
+            a.channels_per_cta = IDENTITY_CHANNELS_PER_CTA;
+            const int64_t groups = (d.Ci + a.channels_per_cta - 1) / a.channels_per_cta;
+            const int64_t id_blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * groups * d.B;
             auto kernel = morpho_backward_identity_kernel<T, IS_MIN, KW>;
-            if (a.copies >= 1 && bytes <= MAX_SHARED_BYTES && allow_shared(kernel, bytes))
+            if (a.copies >= 1 && bytes <= 100 * 1024 && allow_shared(kernel, bytes))
             {
-                kernel<<<static_cast<unsigned>(blocks), THREADS, bytes, stream>>>(a);
+                kernel<<<static_cast<unsigned>(id_blocks), THREADS, bytes, stream>>>(a);
                 return check_launch("morpho_backward_identity_kernel");
             }
         }

@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_regs_kernel(
 {
     using T = float;
     using L = RegsBackwardLayout<KW>;
-    constexpr int WARPS = L::WARPS, TAPS = L::TAPS, FR = L::FR, FC = L::FC, WROW = L::WROW, SLOTS = L::SLOTS;
+    constexpr int TAPS = L::TAPS, FR = L::FR, FC = L::FC, WROW = L::WROW, SLOTS = L::SLOTS;
     constexpr int LEN = segment_len(KW, sizeof(T)), OFF = segment_offset(KW, sizeof(T)), STRIDE = window_stride(KW, sizeof(T));
     static_assert(OFF + FC <= LEN, "a thread's footprint row lies inside its row segment");
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_regs_kernel(
     T* totals = bins + L::BIN_ELEMS;                                               // [channels][TAPS]
 
     // Stage the window (border resolved) and the structuring elements of every output channel, negated for erosion.
-    load_window(foot, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0, tile_w0, a.fill);
+    stage_window_async<STRIDE>(foot, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0, tile_w0, a.fill, [](int c) { return c; });
     {
         const T* wb = a.w + static_cast<int64_t>(b) * g.weight_batch_stride;
         for (int e = threadIdx.x; e < channels * KW * WROW; e += THREADS)
@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(THREADS, 2) morpho_backward_pairs_regs_kernel(
     }
     for (int e = threadIdx.x; e < L::BIN_ELEMS; e += THREADS) bins[e] = T(0);
     for (int e = threadIdx.x; e < channels * TAPS; e += THREADS) totals[e] = T(0);
+    cp_async_wait_all();
     __syncthreads();
 
     // The thread's window: X[r][c] is window row 2 ty + r, column 4 tx + OFF + c, so that tap (kh, kw) of patch pixel
