@@ -450,11 +450,13 @@ def run_case(name, batch, device):
     elif part == "cfg4":
         c = WL.cfg4("dilation", B=batch)
         args, fn = (c["x"], c["w"]), (lambda x, w: F.dilation(x, w, "identity"))
-    elif part in ("cfg5l2", "cfg5l3"):
+    elif part in ("cfg5l2", "cfg5l2pp", "cfg5l3"):
         g = torch.Generator().manual_seed(0)
         x = torch.rand((batch, 64, 224, 224), generator=g)
-        if part == "cfg5l2":
-            args = (x, 0.1 * torch.randn((64, 64, 3, 3), generator=g), torch.full((64, 64), 2.0))
+        if part in ("cfg5l2", "cfg5l2pp"):
+            # "pp": one alpha per pair, as after the first optimiser step of a training run
+            alpha = torch.full((64, 64), 2.0) + (0.01 * torch.randn((64, 64), generator=g) if part == "cfg5l2pp" else 0.0)
+            args = (x, 0.1 * torch.randn((64, 64, 3, 3), generator=g), alpha)
             fn = lambda x, w, a: F.smorph(x, w, a, channel_merge_mode="sum")
         else:
             args, fn = (x, 0.1 * torch.randn((64, 64, 5, 5), generator=g)), (lambda x, w: F.erosion(x, w, "max"))
@@ -495,7 +497,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip configurations 1-4")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--case", default=None, help="profiling helper: run one operator twice and exit, e.g. cfg2_fwd, cfg2_bwd, cfg3_fwd, "
-                    "cfg3_bwd, cfg4_fwd, cfg4_bwd, cfg5l2_fwd, cfg5l2_bwd, cfg5l3_fwd, cfg5l3_bwd (with --case-batch)")
+                    "cfg3_bwd, cfg4_fwd, cfg4_bwd, cfg5l2_fwd, cfg5l2_bwd, cfg5l2pp_fwd, cfg5l2pp_bwd, cfg5l3_fwd, cfg5l3_bwd (with --case-batch)")
     ap.add_argument("--case-batch", type=int, default=4)
     args = ap.parse_args()
 

@@ -1865,3 +1865,5 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
 }
 
 }  // namespace mc
+
+#include "smorph_forward_lean.cuh"

@@ -16,6 +16,16 @@ int smorph_forward<MC_T>(const mc_desc& d, const MC_T* x, const MC_T* w, const M
     const bool wide = d.merge != MC_MERGE_IDENTITY && d.Co >= 2;
     return dispatch_kernel_width(d.kH, d.kW, [&](auto kw) {
         constexpr int KW = decltype(kw)::value;
+        // Float, 3 x 3, SUM / MEAN merge: the kernel built around per-pair alphas; it declines (and launches nothing)
+        // when the input cannot be staged by TMA.
+        if constexpr (std::is_same<T, float>::value && KW == 3)
+        {
+            if (counts == nullptr && d.Co >= 4 && (d.merge == MC_MERGE_ADD || d.merge == MC_MERGE_AVERAGE))
+            {
+                const int rc = launch_smorph_forward_lean<3>(d, x, w, alpha, y, stream);
+                if (rc != MC_ERR_UNSUPPORTED) return rc;
+            }
+        }
         // The factorised path has registers to spare: four output channels share every (E, A) buffer.
         if constexpr (can_factorise<T, KW, false>())
         {
