@@ -208,7 +208,32 @@ __device__ __forceinline__ void stage_weights(T* __restrict__ sw, const T* __res
     }
 }
 
-template <typename T, bool IS_MIN, int KW, int OB, bool TRACK, bool USE_TMA>
+/// Winning channels of the OB output channels of one pixel, packed into 32-bit words: FIELD bits per channel (8 when
+/// there are at most 256 input channels, else 16). Replacing one field is a single byte-permute instruction, and a
+/// pixel costs one or two registers instead of OB: that is what lets the index-tracking kernel keep the packed adds.
+template <int OB, int FIELD> struct PackedWinners
+{
+    static constexpr int PER = 32 / FIELD, WORDS = (OB + PER - 1) / PER;
+    unsigned int word[WORDS];
+    __device__ __forceinline__ void clear()
+    {
+#pragma unroll
+        for (int i = 0; i < WORDS; i++) word[i] = 0u;
+    }
+    /// Field `o` (a compile-time constant after unrolling) := channel.
+    __device__ __forceinline__ void set(int o, unsigned int channel)
+    {
+        const int f = o % PER;
+        unsigned int selector;
+        if (FIELD == 8) selector = f == 0 ? 0x3214u : (f == 1 ? 0x3240u : (f == 2 ? 0x3410u : 0x4210u));
+        else selector = f == 0 ? 0x3254u : 0x5410u;
+        word[o / PER] = __byte_perm(word[o / PER], channel, selector);
+    }
+    __device__ __forceinline__ int get(int o) const { return static_cast<int>((word[o / PER] >> (FIELD * (o % PER))) & ((1u << FIELD) - 1u)); }
+};
+
+/// TRACK: 0 = no winner index, 8 / 16 = track the winning channel of MAX / MIN merges in fields of that many bits.
+template <typename T, bool IS_MIN, int KW, int OB, int TRACK, bool USE_TMA>
 __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1)) ? 1 : 2)
     morpho_forward_kernel(const ForwardArgs<T> a, const __grid_constant__ CUtensorMap tmap)
 {
@@ -242,17 +267,16 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
     const T merge_init = a.merge == MC_MERGE_MAX ? -Limits<T>::max() : (a.merge == MC_MERGE_MIN ? Limits<T>::max() : T(0));
 
     T merged[OB][PATCH_H][PATCH_W];
-    int winner[TRACK ? OB : 1][PATCH_H][PATCH_W];
+    PackedWinners<OB, TRACK ? TRACK : 8> winner[TRACK ? PATCH_H : 1][TRACK ? PATCH_W : 1];
 #pragma unroll
-    for (int o = 0; o < OB; o++)
+    for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-        for (int rr = 0; rr < PATCH_H; rr++)
+        for (int j = 0; j < PATCH_W; j++)
+        {
+            if constexpr (TRACK != 0) winner[rr][j].clear();
 #pragma unroll
-            for (int j = 0; j < PATCH_W; j++)
-            {
-                merged[o][rr][j] = merge_init;
-                if constexpr (TRACK) winner[o][rr][j] = 0;
-            }
+            for (int o = 0; o < OB; o++) merged[o][rr][j] = merge_init;
+        }
 
     // TMA: chunk n + 1 is copied into the other stage while chunk n is computed. The copy zero fills
     // outside the image; tiles whose window leaves the image patch those elements for the other border rules.
@@ -320,21 +344,22 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
 #pragma unroll
                     for (int j = 0; j < PATCH_W; j++) acc[o][rr][j] = op_init;
 
-            // (the index-tracking variant has no registers to spare for the pair copies of the packed adds)
             bool done = false;
             if constexpr (OB >= 2)
             {
                 if (split)
                 {
                     auto& lower = reinterpret_cast<T (&)[OB / 2][PATCH_H][PATCH_W]>(acc);
-                    window_extremum<T, IS_MIN, KW, OB / 2, !TRACK, OB>(lower, sx + c * g.window_elems(), sw + c * g.taps() * OB + o_base, g, tx, ty);
+                    window_extremum<T, IS_MIN, KW, OB / 2, true, OB>(lower, sx + c * g.window_elems(), sw + c * g.taps() * OB + o_base, g, tx, ty);
                     done = true;
                 }
             }
-            if (!done) window_extremum<T, IS_MIN, KW, OB, !TRACK>(acc, sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
+            if (!done) window_extremum<T, IS_MIN, KW, OB, true>(acc, sx + c * g.window_elems(), sw + c * g.taps() * OB, g, tx, ty);
 
             const int ci = c0 + c;
-            // The merge mode is the same for every pixel: one switch around the pixel loops.
+            // The merge mode is the same for every pixel: one switch around the pixel loops. A channel wins a MAX / MIN
+            // merge when it is strictly better than the running value, which starts at the merge's initial value with
+            // channel 0 as the winner (the reference's rule, csrc/cpp/morpho_op_cpu_kernels.hxx:358-360, 389-390).
             auto for_values = [&](auto f) {
 #pragma unroll
                 for (int o = 0; o < OB; o++)
@@ -343,21 +368,23 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
 #pragma unroll
                     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                        for (int j = 0; j < PATCH_W; j++) f(merged[o][rr][j], acc[o][rr][j], winner[TRACK ? o : 0][rr][j]);
+                        for (int j = 0; j < PATCH_W; j++) f(merged[o][rr][j], acc[o][rr][j], winner[TRACK ? rr : 0][TRACK ? j : 0], o);
                 }
             };
             if (a.merge == MC_MERGE_MAX)
-                for_values([&](T& m, T v, int& win) {
-                    if (TRACK && (ci == 0 || v > m)) win = ci;
+                for_values([&](T& m, T v, auto& win, int o) {
+                    if constexpr (TRACK != 0)
+                        if (v > m) win.set(o, static_cast<unsigned int>(ci));
                     m = m < v ? v : m;
                 });
             else if (a.merge == MC_MERGE_MIN)
-                for_values([&](T& m, T v, int& win) {
-                    if (TRACK && (ci == 0 || v < m)) win = ci;
+                for_values([&](T& m, T v, auto& win, int o) {
+                    if constexpr (TRACK != 0)
+                        if (v < m) win.set(o, static_cast<unsigned int>(ci));
                     m = v < m ? v : m;
                 });
-            else if (a.merge == MC_MERGE_IDENTITY) for_values([](T& m, T v, int&) { m = v; });
-            else for_values([](T& m, T v, int&) { m = m + v; });
+            else if (a.merge == MC_MERGE_IDENTITY) for_values([](T& m, T v, auto&, int) { m = v; });
+            else for_values([](T& m, T v, auto&, int) { m = m + v; });
         }
     }
 
@@ -395,12 +422,12 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 && (TRACK || OB > 1))
                         if (w0 + j < g.W) a.y[row + w0 + j] = out[j];
                 }
             }
-            if constexpr (TRACK)
+            if constexpr (TRACK != 0)
             {
-                // Only the winning channel is known here; morpho_find_tap_kernel adds the tap.
+                // Only the winning channel is known here; the tap search kernels add the tap.
 #pragma unroll
                 for (int j = 0; j < PATCH_W; j++)
-                    if (w0 + j < g.W) a.idx[row + w0 + j] = winner[o][rr][j] << 16;
+                    if (w0 + j < g.W) a.idx[row + w0 + j] = winner[rr][j].get(o) << 16;
             }
         }
     }
@@ -466,6 +493,88 @@ __global__ void __launch_bounds__(THREADS) morpho_find_tap_kernel(const ForwardA
     }
 }
 
+/// Tile of the tiled tap search: 16 x 16 output pixels, one per thread.
+constexpr int FIND_TILE = 16;
+
+/// The second step of the winner index for the specialised square widths, without gathers from global memory. The
+/// one-pixel-per-thread scan above reads 25 (5 x 5) scattered elements of a different channel plane per lane: at 64
+/// channels that is an L2 gather of a few hundred bytes per output pixel and takes half as long as the whole
+/// forward pass. Here a CTA owns (batch element, 16 x 16 tile), stages the windows of a group of input channels
+/// (as many as fit in shared memory; every channel for 64 of them at 5 x 5) and then walks ALL output channels:
+/// a thread looks up its pixel's winning channel and scans that channel's window in shared memory, with the
+/// output channel's structuring elements staged beside it. The input is read from global memory once per group
+/// (plus the halo), the indices once, and every scan is the reference's strict comparison in kh-major, kw order.
+template <typename T, bool IS_MIN, int KW>
+__global__ void __launch_bounds__(FIND_TILE * FIND_TILE) morpho_find_tap_tiled_kernel(const ForwardArgs<T> a, int group)
+{
+    static_assert(KW > 0, "specialised widths only");
+    constexpr int WIN = FIND_TILE + KW - 1, TAPS = KW * KW, NT = FIND_TILE * FIND_TILE;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const Geometry& g = a.g;
+    T* sx = reinterpret_cast<T*>(smem_raw);            // [group][WIN][WIN]
+    T* sw = sx + group * WIN * WIN;                    // [group][TAPS] of the current output channel
+
+    const int tiles_x = (g.W + FIND_TILE - 1) / FIND_TILE;
+    const int tile_h0 = (blockIdx.x / tiles_x) * FIND_TILE, tile_w0 = (blockIdx.x % tiles_x) * FIND_TILE;
+    const int b = blockIdx.y;
+    const int tx = threadIdx.x % FIND_TILE, ty = threadIdx.x / FIND_TILE;
+    const int h = tile_h0 + ty, w = tile_w0 + tx;
+    const bool live = h < g.H && w < g.W;
+    const int64_t plane = g.plane();
+    const T op_init = IS_MIN ? Limits<T>::inf() : -Limits<T>::inf();
+    const T* wb = a.w + static_cast<int64_t>(b) * g.weight_batch_stride;
+    const int row0 = tile_h0 - g.halo_top(), col0 = tile_w0 - halo_left_of(KW);
+
+    for (int c0 = 0; c0 < g.Ci; c0 += group)
+    {
+        const int cc = min(group, g.Ci - c0);
+        __syncthreads();   // the previous group's windows are no longer read
+        for (int e = threadIdx.x; e < cc * WIN * WIN; e += NT)
+        {
+            const int c = e / (WIN * WIN), rest = e - c * (WIN * WIN), r = rest / WIN, col = rest - r * WIN;
+            const int iy = row0 + r, ix = col0 + col;
+            const bool in = iy >= 0 && iy < g.H && ix >= 0 && ix < g.W;
+            const T* src = a.x + (static_cast<int64_t>(b) * g.Ci + c0 + c) * plane;
+            if (in || g.replicate) cp_async_element(sx + e, src + static_cast<int64_t>(min(max(iy, 0), g.H - 1)) * g.W + min(max(ix, 0), g.W - 1));
+            else sx[e] = a.fill;
+        }
+        cp_async_wait_all();
+        const int64_t at0 = ((static_cast<int64_t>(b) * g.Co) * g.H + h) * g.W + w;
+        int next = live ? a.idx[at0] : 0;   // the winner of the next output channel is fetched one iteration ahead
+        for (int o = 0; o < g.Co; o++)
+        {
+            __syncthreads();   // windows landed (first pass); the previous output channel's structuring elements are no longer read
+            for (int e = threadIdx.x; e < cc * TAPS; e += NT) sw[e] = __ldg(wb + (static_cast<int64_t>(o) * g.Ci + c0) * TAPS + e);
+            const int packed = next;
+            if (live && o + 1 < g.Co) next = a.idx[at0 + static_cast<int64_t>(o + 1) * plane];
+            __syncthreads();
+            if (!live) continue;
+            const int64_t at = at0 + static_cast<int64_t>(o) * plane;
+            int ch = packed >> 16;
+            ch = min(max(ch, 0), g.Ci - 1);
+            if (ch < c0 || ch >= c0 + cc) continue;
+            const T* win = sx + (ch - c0) * (WIN * WIN) + ty * WIN + tx;
+            const T* wk = sw + (ch - c0) * TAPS;
+            T best = op_init;
+            int arg = 0;
+#pragma unroll
+            for (int kh = 0; kh < KW; kh++)
+#pragma unroll
+                for (int kw = 0; kw < KW; kw++)
+                {
+                    const T xv = win[(KW - 1 - kh) * WIN + KW - 1 - kw], wv = wk[kh * KW + kw];
+                    const T v = IS_MIN ? xv - wv : xv + wv;
+                    if (strictly_better<IS_MIN>(v, best))
+                    {
+                        best = v;
+                        arg = kh * KW + kw;
+                    }
+                }
+            a.idx[at] = (ch << 16) | arg;
+        }
+    }
+}
+
 template <typename T> struct ForwardPlan
 {
     int chunk;
@@ -490,7 +599,7 @@ inline bool plan_forward(const Geometry& g, int ob, int stages, ForwardPlan<T>& 
     return true;
 }
 
-template <typename T, bool IS_MIN, int KW, int OB, bool TRACK, bool USE_TMA>
+template <typename T, bool IS_MIN, int KW, int OB, int TRACK, bool USE_TMA>
 int launch_forward_variant(const ForwardArgs<T>& a, const CUtensorMap& tmap, int64_t blocks, size_t smem, cudaStream_t stream)
 {
     auto kernel = morpho_forward_kernel<T, IS_MIN, KW, OB, TRACK, USE_TMA>;
@@ -529,8 +638,9 @@ int launch_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx,
         && make_window_tensor_map(&tmap, x, sizeof(T), d.B, d.Ci, d.H, d.W, g.win_stride, g.win_rows, plan.chunk))
     {
         a.chunk = plan.chunk;
-        rc = track ? launch_forward_variant<T, IS_MIN, KW, OB, true, true>(a, tmap, blocks, plan.smem, stream)
-                   : launch_forward_variant<T, IS_MIN, KW, OB, false, true>(a, tmap, blocks, plan.smem, stream);
+        rc = !track ? launch_forward_variant<T, IS_MIN, KW, OB, 0, true>(a, tmap, blocks, plan.smem, stream)
+             : (d.Ci <= 256 ? launch_forward_variant<T, IS_MIN, KW, OB, 8, true>(a, tmap, blocks, plan.smem, stream)
+                            : launch_forward_variant<T, IS_MIN, KW, OB, 16, true>(a, tmap, blocks, plan.smem, stream));
     }
     else
     {
@@ -540,10 +650,25 @@ int launch_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx,
             return MC_ERR_UNSUPPORTED;
         }
         a.chunk = plan.chunk;
-        rc = track ? launch_forward_variant<T, IS_MIN, KW, OB, true, false>(a, tmap, blocks, plan.smem, stream)
-                   : launch_forward_variant<T, IS_MIN, KW, OB, false, false>(a, tmap, blocks, plan.smem, stream);
+        rc = !track ? launch_forward_variant<T, IS_MIN, KW, OB, 0, false>(a, tmap, blocks, plan.smem, stream)
+             : (d.Ci <= 256 ? launch_forward_variant<T, IS_MIN, KW, OB, 8, false>(a, tmap, blocks, plan.smem, stream)
+                            : launch_forward_variant<T, IS_MIN, KW, OB, 16, false>(a, tmap, blocks, plan.smem, stream));
     }
     if (rc != MC_OK || !track) return rc;
+    if constexpr (KW > 0)
+    {
+        // Tiled search from shared memory when a useful group of channel windows fits (two CTAs per SM).
+        constexpr size_t WINDOW = static_cast<size_t>(FIND_TILE + KW - 1) * (FIND_TILE + KW - 1) * sizeof(T);
+        constexpr size_t PER_CHANNEL = WINDOW + static_cast<size_t>(KW) * KW * sizeof(T);
+        const int group = static_cast<int>(std::min<size_t>(d.Ci, (110 * 1024) / PER_CHANNEL));
+        const int64_t tiles = static_cast<int64_t>((d.W + FIND_TILE - 1) / FIND_TILE) * ((d.H + FIND_TILE - 1) / FIND_TILE);
+        auto tiled = morpho_find_tap_tiled_kernel<T, IS_MIN, KW>;
+        if (group >= 8 && d.B <= 65535 && tiles <= 0x7fffffffLL && allow_shared(tiled, group * PER_CHANNEL))
+        {
+            tiled<<<dim3(static_cast<unsigned>(tiles), static_cast<unsigned>(d.B)), FIND_TILE * FIND_TILE, group * PER_CHANNEL, stream>>>(a, group);
+            return check_launch("morpho_find_tap_tiled_kernel");
+        }
+    }
     const int64_t total = static_cast<int64_t>(d.B) * d.Co * d.H * d.W;
     const int64_t finder_blocks = std::min<int64_t>((total + THREADS - 1) / THREADS, 148LL * 64);
     morpho_find_tap_kernel<T, IS_MIN><<<static_cast<unsigned>(finder_blocks), THREADS, 0, stream>>>(a, total);

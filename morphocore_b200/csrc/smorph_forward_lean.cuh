@@ -22,9 +22,8 @@
 //     loads them (E = A = 0 follow from the arithmetic; the sentinels are flipped if a later pair of the channel has
 //     the other sign), so the staged window is the raw TMA copy: no border patching pass and no second copy of the
 //     window for pairs of the other sign.
-// A pair whose exponent range |alpha| log2(e) (range of x in the block + range of w) exceeds FACTOR_RANGE binades takes
-// a plain max-subtracting evaluation instead (warp-uniform branch; rare: |alpha| of several hundred, or inputs spread
-// over many decades).
+// A pair whose exponent range |alpha| log2(e) (range of x in the block + range of w) exceeds LEAN_RANGE binades takes the
+// max-subtracting evaluation instead (warp-uniform branch: large |alpha|, or inputs spread widely inside one block).
 #pragma once
 
 namespace mc
@@ -45,6 +44,42 @@ struct LeanForwardArgs
 };
 
 constexpr int LEAN_OB = 4;   // output channels of a CTA: they share the registers that hold the block of x
+// Largest exponent range, in binades, that a pair may span and still be factorised here: every product E_q Ew_k is then at
+// least 2^-112, fourteen binades above the smallest normal float (the exponentials flush denormal results to zero), and
+// the reciprocal of the smallest possible S, 2^112, is far from overflow. Activations of a deep stack (values of a few
+// hundred, spread over tens of units inside one 32 x 8 block) reach 100 binades at |alpha| = 2.
+constexpr float LEAN_RANGE = 112.0f;
+
+/// Soft extrema (u domain) of the four pixels of patch row rr for one 3 x 3 pair, by the max-subtracting evaluation with
+/// the nine candidates of each pixel in registers (smorph3_values, smorph3_softmax: one ex2 per tap). `win` is the raw
+/// window (zeros outside the image): with `masked`, candidates whose tap lies outside the image are excluded here.
+/// Not inlined on purpose: the factorised path around its call site keeps its registers.
+static __device__ __noinline__ float4 lean_stable_row(const float* __restrict__ win, const float* __restrict__ swk, float s, float scale, int H, int W, int h,
+                                               int w0, int tx, int ty, int rr, bool masked)
+{
+    constexpr int LEN = segment_len(3, 4), OFF = segment_offset(3, 4), STRIDE = window_stride(3, 4);
+    float d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+#pragma unroll
+    for (int kh = 0; kh < 3; kh++)
+    {
+        float seg[LEN];
+        load_segment<LEN>(seg, win + (ty * PATCH_H + rr + 2 - kh) * STRIDE + tx * PATCH_W);
+#pragma unroll
+        for (int kw = 0; kw < 3; kw++)
+        {
+            const float wv = swk[(kh * 3 + kw) * LEAN_OB];
+#pragma unroll
+            for (int j = 0; j < PATCH_W; j++)
+            {
+                const int iy = h + 1 - kh, ix = w0 + j + 1 - kw;
+                const bool out = masked && (iy < 0 || iy >= H || ix < 0 || ix >= W);
+                d[kh * 3 + kw][j] = out ? -Limits<float>::big() : fmaf(s, seg[OFF + j + 2 - kw], wv);
+            }
+        }
+    }
+    smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+    return make_float4(ref[0] + out_d[0], ref[1] + out_d[1], ref[2] + out_d[2], ref[3] + out_d[3]);
+}
 
 /// The warp's (E, A) table: ROWS rows of CHUNKS 16-byte chunks (E, A, E, A) of two pixels, chunk q stored at swz(q).
 template <int KW> struct LeanTable
@@ -180,6 +215,9 @@ __global__ void __launch_bounds__(THREADS, 2) smorph_forward_lean_kernel(const L
             if (lane + 32 * i < Tb::PAIRS && iy >= 0 && iy < g.H && ix + e >= 0 && ix + e < g.W) inside_mask |= 1u << (2 * i + e);
     }
     const bool last_sweep = lane + 32 * (SWEEPS - 1) < Tb::PAIRS;   // the last sweep is partial
+    // Does the warp's block of the window lie inside the image (no candidate to exclude)?
+    const bool block_inside = tile_h0 - g.halo_top() + block_row0 >= 0 && tile_h0 - g.halo_top() + block_row0 + Tb::ROWS <= g.H
+                              && tile_w0 - g.halo_left() + block_col0 >= 0 && tile_w0 - g.halo_left() + block_col0 + L::WS <= g.W;
     // Table positions of the chunks 2 t .. of a row that thread column t reads (lean_factor_pair).
     int read_at[L::LEN / 2];
 #pragma unroll
@@ -285,7 +323,7 @@ __global__ void __launch_bounds__(THREADS, 2) smorph_forward_lean_kernel(const L
                 if (o0 + os >= g.Co) break;
                 const float4 par = spar[c * OB + os];   // sign, scale, Mw, range of s w
                 const float s = par.x, scale = par.y;
-                if (x_hi >= x_lo && scale * ((x_hi - x_lo) + par.w) <= FACTOR_RANGE)
+                if (x_hi >= x_lo && scale * ((x_hi - x_lo) + par.w) <= LEAN_RANGE)
                 {
                     const float centre = s > 0.0f ? x_hi : -x_lo;
                     if (!(held_s == s && held_scale == scale))
@@ -326,40 +364,18 @@ __global__ void __launch_bounds__(THREADS, 2) smorph_forward_lean_kernel(const L
                 }
                 else
                 {
-                    // Max-subtracting evaluation, pixel by pixel (kept small: it is the rare path).
+                    // Max-subtracting evaluation (lean_stable_row), kept out of line: its 72 registers of candidates and
+                    // exponentials must not weigh on the factorised path.
                     const float* swk = sw + c * TAPS * OB + os;
-                    const int h0 = tile_h0 + ty * PATCH_H, w0 = tile_w0 + tx * PATCH_W;
-#pragma unroll 1
-                    for (int p = 0; p < PATCH_H * PATCH_W; p++)
+#pragma unroll
+                    for (int rr = 0; rr < PATCH_H; rr++)
                     {
-                        const int rr = p / PATCH_W, j = p - rr * PATCH_W;
-                        const float* origin = win + (ty * PATCH_H + rr) * STRIDE + tx * PATCH_W + L::OFF + j;
-                        float u[TAPS];
-                        float ref = -Limits<float>::big();
-#pragma unroll
-                        for (int kh = 0; kh < KW; kh++)
-#pragma unroll
-                            for (int kw = 0; kw < KW; kw++)
-                            {
-                                const int iy = h0 + rr + KW / 2 - kh, ix = w0 + j + KW / 2 - kw;
-                                const bool in = iy >= 0 && iy < g.H && ix >= 0 && ix < g.W;
-                                const float v = fmaf(s, origin[(KW - 1 - kh) * STRIDE + KW - 1 - kw], swk[(kh * KW + kw) * OB]);
-                                u[kh * KW + kw] = in ? v : -Limits<float>::big();
-                                ref = fmaxf(ref, u[kh * KW + kw]);
-                            }
-                        float sum = 0.0f, weighted = 0.0f;
-#pragma unroll
-                        for (int k = 0; k < TAPS; k++)
-                        {
-                            const float d = u[k] - ref, e = soft_exp(d, scale);
-                            sum += e;
-                            weighted = fmaf(e, d, weighted);
-                        }
-                        const float out = ref + weighted * soft_rcp(sum);
-                        // the selects keep the register array statically indexed
-#pragma unroll
-                        for (int q = 0; q < PATCH_H * PATCH_W; q++)
-                            if (q == p) merged[o][q / PATCH_W][q % PATCH_W] = fmaf(s, out, merged[o][q / PATCH_W][q % PATCH_W]);
+                        const float4 out = lean_stable_row(win, swk, s, scale, g.H, g.W, tile_h0 + ty * PATCH_H + rr, tile_w0 + tx * PATCH_W, tx, ty, rr,
+                                                           !block_inside);
+                        merged[o][rr][0] = fmaf(s, out.x, merged[o][rr][0]);
+                        merged[o][rr][1] = fmaf(s, out.y, merged[o][rr][1]);
+                        merged[o][rr][2] = fmaf(s, out.z, merged[o][rr][2]);
+                        merged[o][rr][3] = fmaf(s, out.w, merged[o][rr][3]);
                     }
                 }
             }
