@@ -208,6 +208,42 @@ def test_cfg5_training_step_matches_reference(golden):
                                        err_msg=f"grad_alpha of layer {n}")
 
 
+def test_compositions_against_the_oracle(F):
+    """opening, closing and sigma_layer against the same chains evaluated by the oracle (merge 'sum' then 'identity' for
+    the first two): the chains of dilations and erosions are bit-exact, the sigmoid blend of sigma_layer agrees to float
+    rounding; gradients of the chained operators against the oracle's backward passes chained by hand."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((2, 3, 21, 35)).astype(np.float32)
+    w1 = (0.4 * rng.standard_normal((4, 3, 3, 3))).astype(np.float32)
+    w2 = (0.4 * rng.standard_normal((4, 1, 5, 5))).astype(np.float32)
+    flip = lambda w: np.ascontiguousarray(w[..., ::-1, ::-1])
+    xt, w1t, w2t = (torch.from_numpy(a).cuda() for a in (x, w1, w2))
+    for padding in ("replicate", "geodesic"):
+        eroded = O.morpho_forward("erosion", x, flip(w1), "sum", padding)
+        want = O.morpho_forward("dilation", eroded, w2, "identity", padding)
+        assert np.array_equal(F.opening(xt, w1t, w2t, "sum", padding).cpu().numpy(), want), padding
+        dilated = O.morpho_forward("dilation", x, w1, "sum", padding)
+        want = O.morpho_forward("erosion", dilated, flip(w2), "identity", padding)
+        assert np.array_equal(F.closing(xt, w1t, w2t, "sum", padding).cpu().numpy(), want), padding
+    alpha = rng.standard_normal((4, 3)).astype(np.float32)
+    soft = 1.0 / (1.0 + np.exp(-alpha.astype(np.float64).mean(1)))
+    ero, dil = O.morpho_forward("erosion", x, flip(w1), "sum"), O.morpho_forward("dilation", x, w1, "sum")
+    want = ero * (1.0 - soft).reshape(1, -1, 1, 1) + dil * soft.reshape(1, -1, 1, 1)
+    got = F.sigma_layer(xt, w1t, torch.from_numpy(alpha).cuda())
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    # gradients of the opening: dilation('identity') backward, then erosion('sum') backward on its input gradient
+    gy = rng.standard_normal((2, 4, 21, 35)).astype(np.float32)
+    xr, w1r, w2r = (t.clone().requires_grad_(True) for t in (xt, w1t, w2t))
+    F.opening(xr, w1r, w2r, "sum").backward(torch.from_numpy(gy).cuda())
+    eroded = O.morpho_forward("erosion", x, flip(w1), "sum")
+    g_mid, g_w2 = O.morpho_backward("dilation", eroded, w2, gy, "identity")
+    g_x, g_w1 = O.morpho_backward("erosion", x, flip(w1), g_mid, "sum")
+    np.testing.assert_allclose(xr.grad.cpu().numpy(), g_x, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(w2r.grad.cpu().numpy(), g_w2, rtol=1e-4, atol=1e-3)
+    np.testing.assert_allclose(w1r.grad.cpu().numpy(), flip(g_w1), rtol=1e-4, atol=1e-3)
+
+
 def test_compositions(F):
     """opening / closing with one shared structuring element and geodesic padding are idempotent and
     (anti-)extensive; sigma_layer blends erosion and dilation (the reference's
