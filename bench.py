@@ -284,9 +284,12 @@ def cfg5_roofline(model, x, device):
         t_b = event_ms(lambda: holder["out"].backward(gy))
         taps = WL.taps(B, co, ci, 224, 224, k, k)
         smorph = kind == "smorph"
-        rows.append((t_f, f"L{n + 1} {kind} forward ({'smorph_forward_kernel' if smorph else 'morpho_forward_kernel'})", taps,
+        fwd_kernel = "smorph_forward_lean_kernel" if smorph else ("morpho_forward_kernel + morpho_find_tap_tiled_kernel" if merge in ("max", "min")
+                                                                  else "morpho_forward_kernel")
+        rows.append((t_f, f"L{n + 1} {kind} forward ({fwd_kernel})", taps,
                      PEAK_GTAPS["smorph_fwd_f32" if smorph else "morph_f32"], (ci + co) * 224 * 224 * 4 * B))
-        bwd_kernel = "smorph_backward_kernel" if smorph else ("morpho_backward_index_kernel" if merge in ("max", "min") else "morpho_backward_pairs_kernel")
+        bwd_kernel = "smorph_backward_kernel" if smorph else ("morpho_backward_scatter_kernel" if merge in ("max", "min")
+                                                              else "morpho_backward_pairs_regs_kernel")
         rows.append((t_b, f"L{n + 1} {kind} backward ({bwd_kernel})", taps, PEAK_GTAPS["smorph_bwd_f32" if smorph else "morph_f32"],
                      2 * (ci + co) * 224 * 224 * 4 * B))
         h = holder["out"].detach()
@@ -493,7 +496,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg1", "cfg2", "cfg3", "cfg4", "all"])
     ap.add_argument("--batch", type=int, default=256, help="global batch of config 5")
-    ap.add_argument("--ref-batch", type=int, default=2, help="images per step of the CPU reference sample")
+    ap.add_argument("--ref-batch", type=int, default=8, help="images per step of the CPU reference sample (the metric is per tap and batch "
+                    "elements are independent: eight images give every host core whole bands of work)")
     ap.add_argument("--no-configs", action="store_true", help="skip configurations 1-4")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--case", default=None, help="profiling helper: run one operator twice and exit, e.g. cfg2_fwd, cfg2_bwd, cfg3_fwd, "
@@ -541,6 +545,12 @@ def main():
                                     "ms_per_step": ms}
         line["probe_gunits_per_s"] = probe
         line["peaks_gtaps"] = dict(PEAK_GTAPS)
+        # A thread block whose bounded wait on a TMA copy ran out returns without writing its tile: a run with such a
+        # block is not a measurement.
+        import morphocore_b200
+        line["device_errors"] = morphocore_b200.device_error_count()
+        if line["device_errors"] != 0:
+            raise SystemExit(f"{line['device_errors']} thread blocks gave up waiting for a TMA copy: the results are invalid")
         emit(line)
     if world > 1:
         import torch.distributed as dist

@@ -4,7 +4,7 @@ TEST / BENCHMARK INFRASTRUCTURE ONLY. Runs in a process of its own because the r
 same torch.ops.morphocore namespace as the CUDA package. Prints one JSON object:
 {"seconds": [per-step times], "n_taps": taps per step, "cores": threads used, "sample": "..."}.
 
-Usage: python oracle/ref_runner.py --workload cfg5 --batch 2 --steps 1 --warmup 1
+Usage: python oracle/ref_runner.py --workload cfg5 --batch 8 --steps 1 --warmup 1
 """
 import argparse
 import json
@@ -69,14 +69,14 @@ def step_fn(workload, batch):
             with torch.no_grad():
                 for p in params:
                     p -= 1e-3 * p.grad
-        return run, WL.cfg5_taps(batch), f"config 5 training step at B={batch} of 256 (per-image cost is constant)"
+        return run, WL.cfg5_taps(batch), f"config 5 training step at B={batch} of 256 (the metric is per tap; batch elements are independent)"
     raise SystemExit(f"unknown workload {workload}")
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="cfg5")
-    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--warmup", type=int, default=1)
     args = ap.parse_args()
