@@ -100,15 +100,8 @@ __device__ __forceinline__ void lean_factor_pair(const float4* __restrict__ rows
     using L = FactorLayout<KW>;
     using Tb = LeanTable<KW>;
     static_assert(PATCH_H == 2, "the row schedule below is written for two patch rows");
-#pragma unroll
-    for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-        for (int j = 0; j < PATCH_W; j++)
-        {
-            acc[rr][j] = make_float2(0.0f, 0.0f);
-            rest[rr][j] = 0.0f;
-        }
-    // Table row r (relative to the thread's first patch row) is read by patch row rr through kernel row kh = rr + KW - 1 - r.
+    // Table row r (relative to the thread's first patch row) is read by patch row rr through kernel row kh = rr + KW - 1 - r:
+    // both patch rows meet kernel row KW - 1 first, whose first tap initialises the sums (no zeroing pass).
     auto row = [&](int r, bool first, bool second) {
         float2 seg[L::LEN];
         const float4* src = rows + r * Tb::CHUNKS;
@@ -129,8 +122,16 @@ __device__ __forceinline__ void lean_factor_pair(const float4* __restrict__ rows
                 for (int j = 0; j < PATCH_W; j++)
                 {
                     const float2 q = seg[L::OFF + j + KW - 1 - kw];
-                    acc[rr][j] = __ffma2_rn(q, ew2, acc[rr][j]);
-                    rest[rr][j] = fmaf(q.x, t.y, rest[rr][j]);
+                    if (kh == KW - 1 && kw == 0)
+                    {
+                        acc[rr][j] = __fmul2_rn(q, ew2);
+                        rest[rr][j] = q.x * t.y;
+                    }
+                    else
+                    {
+                        acc[rr][j] = __ffma2_rn(q, ew2, acc[rr][j]);
+                        rest[rr][j] = fmaf(q.x, t.y, rest[rr][j]);
+                    }
                 }
             }
         };
@@ -302,14 +303,29 @@ __global__ void __launch_bounds__(THREADS, 2) smorph_forward_lean_kernel(const L
             {
                 const float2 v = *reinterpret_cast<const float2*>(win + src_at[i]);
                 X[i][0] = v.x; X[i][1] = v.y;
+            }
+            if (block_inside)
+            {
+                // Nothing to exclude (the clamped extra pair of a lane past the end of the block repeats the last one).
 #pragma unroll
-                for (int e = 0; e < 2; e++)
+                for (int i = 0; i < SWEEPS; i++)
                 {
-                    const bool in = (inside_mask >> (2 * i + e)) & 1u;
-                    x_lo = fminf(x_lo, in ? X[i][e] : Limits<float>::inf());
-                    x_hi = fmaxf(x_hi, in ? X[i][e] : -Limits<float>::inf());
-                    X[i][e] = in ? X[i][e] : -x_sign * Limits<float>::big();
+                    x_lo = fminf(x_lo, fminf(X[i][0], X[i][1]));
+                    x_hi = fmaxf(x_hi, fmaxf(X[i][0], X[i][1]));
                 }
+            }
+            else
+            {
+#pragma unroll
+                for (int i = 0; i < SWEEPS; i++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++)
+                    {
+                        const bool in = (inside_mask >> (2 * i + e)) & 1u;
+                        x_lo = fminf(x_lo, in ? X[i][e] : Limits<float>::inf());
+                        x_hi = fmaxf(x_hi, in ? X[i][e] : -Limits<float>::inf());
+                        X[i][e] = in ? X[i][e] : -x_sign * Limits<float>::big();
+                    }
             }
             x_lo = from_ordered(__reduce_min_sync(0xffffffffu, to_ordered(x_lo)));
             x_hi = from_ordered(__reduce_max_sync(0xffffffffu, to_ordered(x_hi)));
