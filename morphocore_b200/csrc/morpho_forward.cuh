@@ -77,7 +77,58 @@ __device__ __forceinline__ void window_extremum(T (&acc)[OB][PATCH_H][PATCH_W], 
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++) load_segment<LEN>(seg[rr], base + (rr + KW - 1 - kh) * STRIDE);
             const T* wrow = wk + kh * KW * WS;
-            if constexpr (sizeof(T) == 4 && PACKED && PACKED_ADD)
+            if constexpr (sizeof(T) == 4 && PACKED && PACKED_ADD && OB % 2 == 0)
+            {
+                // Packed adds (add.f32x2) over PAIRS OF OUTPUT CHANNELS: (x, x) + (w[o], w[o + 1]). The structuring elements
+                // are staged [tap][channel], so a pair of them is a register pair as loaded; only x has to be doubled, one
+                // register move per window element and kernel row, shared by every tap and channel pair that reads it.
+                float2 xx[PATCH_H][PATCH_W + KW - 1];
+#pragma unroll
+                for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                    for (int c = 0; c < PATCH_W + KW - 1; c++) xx[rr][c] = make_float2(seg[rr][OFF + c], seg[rr][OFF + c]);
+#pragma unroll
+                for (int kw = 0; kw + 1 < KW; kw += 2)
+                {
+                    T w0[OB], w1[OB];
+                    load_weights<OB>(w0, wrow + kw * WS);
+                    load_weights<OB>(w1, wrow + (kw + 1) * WS);
+#pragma unroll
+                    for (int o = 0; o < OB; o += 2)
+                    {
+                        const float2 wa = make_float2(w0[o], w0[o + 1]), wb = make_float2(w1[o], w1[o + 1]);
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                            for (int j = 0; j < PATCH_W; j++)
+                            {
+                                const float2 va = __fadd2_rn(xx[rr][j + KW - 1 - kw], wa), vb = __fadd2_rn(xx[rr][j + KW - 2 - kw], wb);
+                                acc[o][rr][j] = ext3<IS_MIN>(acc[o][rr][j], va.x, vb.x);
+                                acc[o + 1][rr][j] = ext3<IS_MIN>(acc[o + 1][rr][j], va.y, vb.y);
+                            }
+                    }
+                }
+                if constexpr (KW & 1)
+                {
+                    T w0[OB];
+                    load_weights<OB>(w0, wrow + (KW - 1) * WS);
+#pragma unroll
+                    for (int o = 0; o < OB; o += 2)
+                    {
+                        const float2 wa = make_float2(w0[o], w0[o + 1]);
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                            for (int j = 0; j < PATCH_W; j++)
+                            {
+                                const float2 va = __fadd2_rn(xx[rr][j], wa);
+                                acc[o][rr][j] = ext2<IS_MIN>(acc[o][rr][j], va.x);
+                                acc[o + 1][rr][j] = ext2<IS_MIN>(acc[o + 1][rr][j], va.y);
+                            }
+                    }
+                }
+            }
+            else if constexpr (sizeof(T) == 4 && PACKED && PACKED_ADD)
             {
                 // Packed adds (add.f32x2): two adjacent pixels per instruction. Pixel pairs start at segment
                 // element OFF + j + KW-1-kw (j = 0, 2); even starts are register pairs as loaded, odd starts
