@@ -177,6 +177,11 @@ __device__ __forceinline__ void cp_async_element(T* dst, const T* src)
     if constexpr (sizeof(T) == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
 }
+/// Asynchronous copy of 16 bytes (both addresses 16-byte aligned), bypassing L1.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 /// load_window with every copy of a thread in flight at once: in-image (or clamped, for REPLICATE) elements travel by

@@ -1199,6 +1199,7 @@ struct SmorphBackwardArgs
     const T* soft_inv;  // smooth merge: 1 / sum_i q_i per output pixel
     T* gbeta;           // smooth merge: gradient of beta
     int o_chunk;      // output channels whose weights and bins are staged together
+    int grad_stage;   // byte offset in shared memory of the per-thread staging slots of grad_output, 0 = read it with plain loads
     T scale;          // 1 / Ci for AVERAGE
     int factorise;    // 5 x 5 and 7 x 7 float kernels: S and N of a pair from the factorised sums where that is safe
     int bounded;      // 3 x 3 float kernels: exponentials relative to a bound of the patch where that is safe
@@ -1481,6 +1482,11 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     load_window_signed(has_pos ? sx : nullptr, has_neg ? sx + welems : nullptr, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0,
                        tile_w0);
     for (int e = threadIdx.x; e < welems; e += THREADS) sg[e] = T(0);
+    if (a.grad_stage != 0)
+    {
+        float4* zero = reinterpret_cast<float4*>(smem_raw + a.grad_stage);
+        for (int e = threadIdx.x; e < 2 * THREADS * PATCH_H * PATCH_W / 4; e += THREADS) zero[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
 
     bool live[PATCH_H][PATCH_W];
     int64_t at0[PATCH_H];
@@ -1611,6 +1617,25 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             // The 3 x 3 float kernel has no registers to spare for the next channel's gradients (it spills at 128): its
             // loads are covered by the other warps instead.
             constexpr bool PREFETCH = !(KH == 3 && sizeof(T) == 4);
+            // Kernels without registers to spare for the next channel's gradients (PREFETCH false) stage them instead: the
+            // thread's two 16-byte rows of the NEXT output channel travel by cp.async into a private slot of shared memory
+            // while the current channel computes, and are read from there when their turn comes (rows outside the image
+            // are never copied and stay zero).
+            [[maybe_unused]] float* slots = nullptr;
+            [[maybe_unused]] int staged = 0;
+            if constexpr (!PREFETCH)
+            {
+                if (a.grad_stage != 0)
+                {
+                    slots = reinterpret_cast<float*>(smem_raw + a.grad_stage) + threadIdx.x * (PATCH_H * PATCH_W);
+                    if (half < oc)
+                    {
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+                            if (live[rr][0]) cp_async_16(slots + rr * PATCH_W, a.gy + at0[rr] + static_cast<int64_t>(oc0 + half) * plane);
+                    }
+                }
+            }
             T grad[PATCH_H][PATCH_W];
             [[maybe_unused]] T next[PREFETCH ? PATCH_H : 1][PREFETCH ? PATCH_W : 1];
             if constexpr (PREFETCH)
@@ -1621,6 +1646,28 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                 if constexpr (PREFETCH)
                 {
                     if (oo + o_step < oc) load_grad(o + o_step, next);  // the next channel's gradients arrive while this one computes
+                }
+                else if (slots != nullptr)
+                {
+                    if constexpr (sizeof(T) == 4)
+                    {
+                        cp_async_wait_all();
+                        const float* slot = slots + (staged & 1) * (THREADS * PATCH_H * PATCH_W);
+#pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+                        {
+                            const float4 q = *reinterpret_cast<const float4*>(slot + rr * PATCH_W);
+                            grad[rr][0] = q.x * a.scale; grad[rr][1] = q.y * a.scale; grad[rr][2] = q.z * a.scale; grad[rr][3] = q.w * a.scale;
+                        }
+                        staged++;
+                        if (oo + o_step < oc)
+                        {
+                            float* next_slot = slots + (staged & 1) * (THREADS * PATCH_H * PATCH_W);
+#pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
+                                if (live[rr][0]) cp_async_16(next_slot + rr * PATCH_W, a.gy + at0[rr] + static_cast<int64_t>(o + o_step) * plane);
+                        }
+                    }
                 }
                 else load_grad(o, grad);
                 const T s = spar[oo * 3], abs_alpha = spar[oo * 3 + 1], scale = spar[oo * 3 + 2];
@@ -1841,6 +1888,10 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
         fixed += 32;
         per_o += sizeof(float2);
     }
+    // Staging slots of grad_output for the 3 x 3 float kernel: two buffers of 32 bytes per thread, after everything else.
+    constexpr size_t GRAD_SLOTS = 2 * THREADS * PATCH_H * PATCH_W * sizeof(float);
+    const bool stage_grad = sizeof(T) == 4 && KH == 3 && KW == 3 && d.W % 4 == 0 && reinterpret_cast<uintptr_t>(gy) % 16 == 0;
+    if (stage_grad) fixed += GRAD_SLOTS + 16;
     if (fixed + per_o > MAX_SHARED_BYTES)
     {
         set_last_error("structuring element %dx%d too large for shared memory", d.kH, d.kW);
@@ -1853,6 +1904,7 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     chunk = std::max(1, std::min(chunk, a.g.identity ? 1 : d.Co));
     a.o_chunk = chunk;
     const size_t smem = fixed + per_o * chunk;
+    a.grad_stage = stage_grad ? static_cast<int>((smem - GRAD_SLOTS) / 16 * 16) : 0;
     const int64_t blocks = static_cast<int64_t>(a.g.tiles_x) * a.g.tiles_y * d.Ci * d.B;
     if (blocks > 0x7fffffffLL) { set_last_error("too many tiles for one launch"); return MC_ERR_UNSUPPORTED; }
     auto launch = [&](auto kernel) {
