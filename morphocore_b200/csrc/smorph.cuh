@@ -1355,16 +1355,23 @@ __device__ __forceinline__ void smorph_taps_backward(const float* __restrict__ w
 {
     constexpr int LEN = segment_len(KW, 4), OFF = segment_offset(KW, 4), STRIDE = window_stride(KW, 4);
     static_assert(KW <= RED_ROWS, "one scratch row per tap of a kernel row");
-    float steep[PATCH_H][PATCH_W], spread[PATCH_H][PATCH_W], minus_centre[PATCH_H][PATCH_W];
+    // Two horizontally adjacent pixels per step: apart from the first difference (scalar, so that the pair is assembled
+    // without register moves), the exponentials and the register window of grad_input, every operation is a packed
+    // two-lane instruction (add / mul / fma.f32x2).
+    float2 steep[PATCH_H][PATCH_W / 2], scaled2[PATCH_H][PATCH_W / 2], spread[PATCH_H][PATCH_W / 2];
+    float minus_centre[PATCH_H][PATCH_W];
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-        for (int j = 0; j < PATCH_W; j++)
+        for (int jp = 0; jp < PATCH_W / 2; jp++)
         {
-            steep[rr][j] = abs_alpha * scaled[rr][j];
-            spread[rr][j] = 0.0f;
-            minus_centre[rr][j] = -centre[rr][j];
+            scaled2[rr][jp] = make_float2(scaled[rr][2 * jp], scaled[rr][2 * jp + 1]);
+            steep[rr][jp] = make_float2(abs_alpha * scaled[rr][2 * jp], abs_alpha * scaled[rr][2 * jp + 1]);
+            spread[rr][jp] = make_float2(0.0f, 0.0f);
+            minus_centre[rr][2 * jp] = -centre[rr][2 * jp];
+            minus_centre[rr][2 * jp + 1] = -centre[rr][2 * jp + 1];
         }
+    const float2 scale2 = make_float2(scale, scale);
 #pragma unroll
     for (int kh = 0; kh < KW; kh++)
     {
@@ -1376,21 +1383,26 @@ __device__ __forceinline__ void smorph_taps_backward(const float* __restrict__ w
         for (int kw = 0; kw < KW; kw++)
         {
             const float wv = swk[kh * KW + kw];
-            float sum = 0.0f;
+            const float2 wv2 = make_float2(wv, wv);
+            float2 sum = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-                for (int j = 0; j < PATCH_W; j++)
+                for (int jp = 0; jp < PATCH_W / 2; jp++)
                 {
-                    const float t = fmaf(s, seg[rr][OFF + j + KW - 1 - kw], minus_centre[rr][j]) + wv;   // as in smorph_pair
-                    const float e = soft_exp(t, scale);   // exactly 0 for an excluded tap (t = -1e30)
-                    const float et = e * t;               // e first: an excluded tap gives 0 * -1e30 = -0, never an overflow
-                    const float c = fmaf(steep[rr][j], et, e * scaled[rr][j]);
-                    gxr[rr + KW - 1 - kh][j + KW - 1 - kw] += c;
-                    sum += c;
-                    spread[rr][j] = fmaf(et, t, spread[rr][j]);
+                    const int j = 2 * jp, at = OFF + j + KW - 1 - kw;
+                    // t = (s x - centre) + s w, as in smorph_pair
+                    const float2 t = __fadd2_rn(make_float2(fmaf(s, seg[rr][at], minus_centre[rr][j]), fmaf(s, seg[rr][at + 1], minus_centre[rr][j + 1])), wv2);
+                    const float2 arg = __fmul2_rn(t, scale2);
+                    const float2 e = make_float2(ex2_approx(arg.x), ex2_approx(arg.y));   // exactly 0 for an excluded tap (t = -1e30)
+                    const float2 et = __fmul2_rn(e, t);   // e first: an excluded tap gives 0 * -1e30 = -0, never an overflow
+                    const float2 c = __ffma2_rn(steep[rr][jp], et, __fmul2_rn(e, scaled2[rr][jp]));
+                    gxr[rr + KW - 1 - kh][j + KW - 1 - kw] += c.x;
+                    gxr[rr + KW - 1 - kh][j + KW - kw] += c.y;
+                    sum = __fadd2_rn(sum, c);
+                    spread[rr][jp] = __ffma2_rn(et, t, spread[rr][jp]);
                 }
-            tap_sum[kw] = sum;
+            tap_sum[kw] = sum.x + sum.y;
         }
         __syncwarp();
 #pragma unroll
@@ -1412,7 +1424,8 @@ __device__ __forceinline__ void smorph_taps_backward(const float* __restrict__ w
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
-        for (int j = 0; j < PATCH_W; j++) alpha_sum = fmaf(spread[rr][j], scaled[rr][j], alpha_sum);
+        for (int jp = 0; jp < PATCH_W / 2; jp++)
+            alpha_sum = fmaf(spread[rr][jp].y, scaled[rr][2 * jp + 1], fmaf(spread[rr][jp].x, scaled[rr][2 * jp], alpha_sum));
     alpha_sum = warp_sum(alpha_sum);
     if (lane == 0) *abin = alpha_sum;
 }
