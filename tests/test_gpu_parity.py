@@ -120,6 +120,22 @@ def test_saved_indices_equal_recomputed(C):
             np.testing.assert_allclose(a[1].cpu().numpy(), wgw, rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_winner_index_with_many_input_channels(C, dtype):
+    """The tiled tap search stages the windows of a GROUP of input channels in shared memory; with more channels than
+    fit (70 in double at 5 x 5: three groups) every pixel must still be searched exactly once, in the group that holds
+    its winning channel. Indices and values against the oracle, both operations, both merges."""
+    rng = np.random.default_rng(23)
+    x = rng.standard_normal((2, 70, 21, 40)).astype(dtype)
+    w = (0.5 * rng.standard_normal((3, 70, 5, 5))).astype(dtype)
+    for op in ("dilation", "erosion"):
+        for merge in ("max", "min"):
+            want, want_idx = O.morpho_forward(op, x, w, merge, "replicate", with_index=True)
+            got, got_idx = C.morpho_forward(op, dev(x), dev(w), merge, "replicate", with_index=True)
+            assert np.array_equal(got.cpu().numpy(), want), (op, merge)
+            assert np.array_equal(got_idx.cpu().numpy(), want_idx), (op, merge)
+
+
 def test_ties_route_to_first_tap_and_channel_zero(C):
     """All-equal input: tap (0, 0) and channel 0 take every gradient; with replicate padding grad_weight
     receives all 25 contributions of a 5 x 5 image but grad_input only those whose tap (0, 0) is inside."""

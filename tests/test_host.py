@@ -18,6 +18,18 @@ def test_enum_integers_match_the_operator_schema():
     assert MorphoMerge.SMOOTH == 4 and MorphoPadding.REPLICATE == 3
 
 
+def test_reference_package_name_resolves_to_this_implementation():
+    """`import morphocore.functional` / `import morphocore.nn` (the reference's names, used by its own tests and by its
+    users) serve the B200 functions and modules."""
+    import morphocore
+    import morphocore.functional as RF
+    import morphocore.nn as RN
+    from morphocore.nn import Closing, Opening
+    assert RF.dilation is F.dilation and RF.erosion is F.erosion and RF.smorph is F.smorph and RF.sigma_layer is F.sigma_layer
+    assert RN.Dilation is Mnn.Dilation and RN.SMorph is Mnn.SMorph and Opening is Mnn.Opening and Closing is Mnn.Closing
+    assert morphocore.__version__ == M.__version__
+
+
 def test_unknown_modes_raise_value_error():
     with pytest.raises(ValueError, match="Unknown merge mode"):
         str_to_merge("average")
