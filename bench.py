@@ -346,6 +346,11 @@ def run_single(name, device, steps, warmup):
         g = n_taps / (f_ms + b_ms) / 1e6
         r = {"gtaps_per_s": g, "fwd_ms": f_ms, "bwd_ms": b_ms, "n_taps": n_taps, "frac_of_peak": g / PEAK_GTAPS[peak_key],
              "peak_gtaps": PEAK_GTAPS[peak_key], "fwd_gtaps_per_s": n_taps / f_ms / 1e6}
+        if bwd_inputs is not None and peak_key.startswith("morph"):
+            # The dilation / erosion backward has to evaluate every tap again (no winner is saved for sum / mean / identity
+            # merges): a forward+backward pair is two passes at the add + max rate.
+            r["pair_peak_gtaps"] = PEAK_GTAPS[peak_key] / 2
+            r["frac_of_pair_peak"] = g / r["pair_peak_gtaps"]
         r.update(extra)
         return r
 
