@@ -387,9 +387,24 @@ int64_t checked_padding(int64_t padding)
     return padding;
 }
 
+/// float16 / bfloat16 tensors: half precision is a STORAGE type here. The operators widen to float, run the float
+/// kernels and narrow the result; they are composite operators, so autograd differentiates through the two casts
+/// and the gradients come back in the input's type. The reference accepts float and double only ("TODO: Add float16
+/// support", csrc/cpp/morpho_op.cpp:7). Every tensor argument must share the input's type.
+bool is_reduced(const torch::Tensor& t) { return t.scalar_type() == torch::kHalf || t.scalar_type() == torch::kBFloat16; }
+
+torch::Tensor widen(const torch::Tensor& t, const torch::Tensor& like, const char* what)
+{
+    TORCH_CHECK(t.scalar_type() == like.scalar_type(), what, " must have the input's dtype (", like.scalar_type(), "), got ", t.scalar_type());
+    return t.to(torch::kFloat);
+}
+
 torch::Tensor dilation(torch::Tensor input, torch::Tensor weight, int64_t merge, int64_t padding, double padding_value, bool save_indices,
                        double noise_scale)
 {
+    if (is_reduced(input))
+        return dilation(input.to(torch::kFloat), widen(weight, input, "weight"), merge, padding, padding_value, save_indices, noise_scale)
+            .to(input.scalar_type());
     return MorphoFunction::apply(input, weight, static_cast<int64_t>(MC_OP_DILATION), checked_merge(merge), checked_padding(padding), padding_value,
                                  save_indices, noise_scale);
 }
@@ -397,6 +412,9 @@ torch::Tensor dilation(torch::Tensor input, torch::Tensor weight, int64_t merge,
 torch::Tensor erosion(torch::Tensor input, torch::Tensor weight, int64_t merge, int64_t padding, double padding_value, bool save_indices,
                       double noise_scale)
 {
+    if (is_reduced(input))
+        return erosion(input.to(torch::kFloat), widen(weight, input, "weight"), merge, padding, padding_value, save_indices, noise_scale)
+            .to(input.scalar_type());
     return MorphoFunction::apply(input, weight, static_cast<int64_t>(MC_OP_EROSION), checked_merge(merge), checked_padding(padding), padding_value,
                                  save_indices, noise_scale);
 }
@@ -404,11 +422,16 @@ torch::Tensor erosion(torch::Tensor input, torch::Tensor weight, int64_t merge, 
 torch::Tensor smorph(torch::Tensor input, torch::Tensor weight, torch::Tensor alpha, int64_t merge)
 {
     TORCH_CHECK(merge >= 0 && merge <= MC_MERGE_IDENTITY && merge != MC_MERGE_SMOOTH, "Unsupported merge operation for smorph");
+    if (is_reduced(input))
+        return smorph(input.to(torch::kFloat), widen(weight, input, "weight"), widen(alpha, input, "alpha"), merge).to(input.scalar_type());
     return SmorphFunction::apply(input, weight, alpha, merge);
 }
 
 torch::Tensor smorph_scm(torch::Tensor input, torch::Tensor weight, torch::Tensor alpha, torch::Tensor beta)
 {
+    if (is_reduced(input))
+        return smorph_scm(input.to(torch::kFloat), widen(weight, input, "weight"), widen(alpha, input, "alpha"), widen(beta, input, "beta"))
+            .to(input.scalar_type());
     return SmorphScmFunction::apply(input, weight, alpha, beta);
 }
 

@@ -100,6 +100,36 @@ def test_smorph_scm_matches_golden_and_gradcheck(F, manifest, golden):
         F.smorph(x, w, a, beta=torch.zeros(3, dtype=torch.float64, device="cuda"))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_half_precision_storage(F, dtype):
+    """float16 / bfloat16 tensors (not accepted by the reference): the operators compute in float and round once, so
+    values and gradients equal the float run on the same (widened) tensors, rounded to the storage type."""
+    torch.manual_seed(6)
+    x = torch.randn(2, 3, 20, 36, device="cuda").to(dtype)
+    w = (0.3 * torch.randn(4, 3, 3, 3, device="cuda")).to(dtype)
+    a = torch.tensor([[1.5, -2.0, 0.5]] * 4, device="cuda").to(dtype)
+    gy = torch.randn(2, 4, 20, 36, device="cuda").to(dtype)
+    calls = [lambda p, q, r: F.dilation(p, q, "sum"), lambda p, q, r: F.erosion(p, q, "max", "geodesic"),
+             lambda p, q, r: F.smorph(p, q, r, channel_merge_mode="mean")]
+    for n, call in enumerate(calls):
+        lo = [t.clone().requires_grad_(True) for t in (x, w, a)]
+        hi = [t.float().requires_grad_(True) for t in (x, w, a)]
+        y_lo, y_hi = call(*lo), call(*hi)
+        assert y_lo.dtype == dtype
+        y_lo.backward(gy)
+        y_hi.to(dtype).backward(gy)   # the same narrowing of the output as in the half-precision call
+        if n < 2:   # dilation / erosion: the operator is all there is between the tensors and the result
+            assert torch.equal(y_lo, y_hi.to(dtype))
+            for p, q in zip(lo[:2], hi[:2]):
+                assert p.grad.dtype == dtype and torch.equal(p.grad, q.grad.to(dtype))
+        else:       # smorph: the Python re-parametrisation of the structuring element runs in the storage type
+            tol = dict(rtol=5e-2, atol=5e-2)
+            torch.testing.assert_close(y_lo.float(), y_hi, **tol)
+            torch.testing.assert_close(lo[0].grad.float(), hi[0].grad, **tol)
+    with pytest.raises(RuntimeError, match="must have the input's dtype"):
+        F.dilation(x, w.float())
+
+
 def test_lower_dimensional_inputs(F):
     x2 = torch.randn(9, 8, device="cuda", requires_grad=True)
     w2 = torch.randn(3, 3, device="cuda", requires_grad=True)

@@ -370,6 +370,36 @@ def test_smorph_factorised_backward_matches_double(C, case, merge):
     torch.testing.assert_close(ga.double(), ra, rtol=1e-4 * amp, atol=1e-4 * amp * float(ra.abs().max()))
 
 
+@pytest.mark.parametrize("merge", ["max", "min"])
+@pytest.mark.parametrize("k", [3, 5])
+def test_smorph_winner_merges_at_scale(C, merge, k):
+    """MAX / MIN merges of smorph on a larger problem (16 input channels, 8 output channels, several tiles with partial
+    ones): the float kernels against the double kernels. Only the channels within 1e-6 of the merged value receive
+    gradient, shared equally (csrc/cpp/smorph_cpu_kernels.hxx:507-519): pixels whose runner-up channel is closer than 1e-5
+    are excluded from the gradient comparison, as in test_smorph_against_oracle, because rounding decides their side."""
+    g = torch.Generator().manual_seed(99 + k)
+    B, Ci, Co, H, W = 2, 16, 8, 96, 130
+    x = torch.randn((B, Ci, H, W), generator=g).cuda()
+    w = (0.3 * torch.randn((Co, Ci, k, k), generator=g)).cuda()
+    a = (2.0 * torch.randn((Co, Ci), generator=g)).cuda()
+    gy = torch.randn((B, Co, H, W), generator=g).cuda()
+    xd, wd, ad = x.double(), w.double(), a.double()
+    per_channel = torch.stack([C.smorph_forward(xd[:, i:i + 1].contiguous(), wd[:, i:i + 1].contiguous(), ad[:, i:i + 1].contiguous(), "sum")
+                               for i in range(Ci)])
+    ordered = per_channel.sort(0).values
+    gap = (ordered[1] - ordered[0]) if merge == "min" else (ordered[-1] - ordered[-2])
+    gy = torch.where(gap < 1e-5, torch.zeros_like(gy), gy)
+    y = C.smorph_forward(x, w, a, merge)
+    yd = C.smorph_forward(xd, wd, ad, merge)
+    torch.testing.assert_close(y.double(), yd, rtol=1e-4, atol=1e-5)
+    gx, gw, ga = C.smorph_backward(x, w, a, y, gy, merge)
+    rx, rw, ra = C.smorph_backward(xd, wd, ad, yd, gy.double(), merge)
+    amp = max(1.0, float(a.abs().max()) / 10.0)
+    torch.testing.assert_close(gx.double(), rx, rtol=1e-4 * amp, atol=3e-5 * amp)
+    torch.testing.assert_close(gw.double(), rw, rtol=1e-4 * amp, atol=1e-4 * amp * float(rw.abs().max()))
+    torch.testing.assert_close(ga.double(), ra, rtol=1e-4 * amp, atol=1e-4 * amp * float(ra.abs().max()))
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("k", [3, 5, (4, 3), 11])
 def test_smorph_scm_against_oracle(C, k, dtype):
