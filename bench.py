@@ -43,8 +43,9 @@ UNIT = "Gtaps/s"
 # below are an earlier measurement on this pool's B200 (profiles/probe_rates_b200.md), used only when the
 # probe binary is missing. A dilation / erosion tap is one add and one max; the float peak is the best mix
 # found (packed add.f32x2 + 3-input max), the double peak DADD + compare/select; a smorph tap costs three
-# fused multiply-adds forward (factorised exponentials) and eleven FP32 operations plus one ex2 backward.
-PEAK_GTAPS = {"morph_f32": 27300.0, "morph_f64": 5750.0, "smorph_fwd_f32": 10078.0, "smorph_bwd_f32": 2748.0, "smorph_fwdbwd_f32": 2159.0}
+# fused multiply-adds forward (factorised exponentials) and ten FP32 operations plus one ex2 backward. Packed
+# two-lane instructions halve the issue slots of an operation, not its time on the FP32 pipe: both count per lane.
+PEAK_GTAPS = {"morph_f32": 27300.0, "morph_f64": 5750.0, "smorph_fwd_f32": 10844.0, "smorph_bwd_f32": 3253.0, "smorph_fwdbwd_f32": 2502.0}
 PEAK_SOURCE = "earlier measurement on this pool (probe binary missing)"
 
 
@@ -60,11 +61,12 @@ def measure_peaks():
         PEAK_GTAPS["morph_f32"] = max(r["add_max_taps"], r["add_max3_taps"], r["add2_max3_taps"])
         PEAK_GTAPS["morph_f64"] = max(r["f64_add_fmax_taps"], r["f64_add_select_taps"])
         # smorph forward (sum / mean / identity merges): the factorised kernel needs 3 fused multiply-adds per tap and
-        # no exponential; smorph backward: 11 FP32 operations (u, d, scale, sum e, e d, sum e d, sum e d^2, two for c_k,
-        # grad_input and grad_weight accumulation) and one ex2 per tap.
+        # no exponential; smorph backward: 10 FP32 operations (the exponent t, sum e, e t, sum e t, sum e t^2, two for
+        # c_k, grad_input and grad_weight accumulation: nine per tap, plus one fma per window element and six
+        # operations per pixel, together one more per tap at 3 x 3) and one ex2 per tap.
         fma = max(r["fma_ops"], r.get("fma2_ops", 0.0))
         PEAK_GTAPS["smorph_fwd_f32"] = fma / 3
-        PEAK_GTAPS["smorph_bwd_f32"] = min(r["ex2_ops"], fma / 11)
+        PEAK_GTAPS["smorph_bwd_f32"] = min(r["ex2_ops"], fma / 10)
         PEAK_GTAPS["smorph_fwdbwd_f32"] = 1.0 / (1.0 / PEAK_GTAPS["smorph_fwd_f32"] + 1.0 / PEAK_GTAPS["smorph_bwd_f32"])
         PEAK_SOURCE = "of measured (instruction-rate probe run on this GPU at the start of this bench)"
         return r

@@ -13,6 +13,8 @@
 // exponent scale is clamped to 1e-20 from below so that this also holds for alpha = 0). Excluded taps
 // therefore cost no instruction.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 #include "morpho_backward.cuh"
 #include "tma.cuh"
@@ -520,13 +522,18 @@ __device__ __forceinline__ float ex2_approx(float x)
     return e;
 }
 
+/// Register window of grad_input of the 3 x 3 float kernels: (PATCH_H + 2) rows of three column pairs, so that the
+/// contributions of the taps with an even column offset are one packed add per pair of pixels.
+using GradWindow3 = float2[PATCH_H + 2][(PATCH_W + 2) / 2];
+__device__ __forceinline__ float& window_at(GradWindow3& w, int r, int c) { return (c & 1) ? w[r][c >> 1].y : w[r][c >> 1].x; }
+
 /// float version of smorph3_pair_backward on pairs of horizontally adjacent pixels: apart from the values
 /// u_k, the maximum, the exponentials and the register window of grad_input, every step is a packed
 /// two-lane instruction (add.f32x2, mul.f32x2, fma.rn.f32x2), half the issue slots of the scalar form.
 __device__ __forceinline__ void smorph3_pair_backward(const float* __restrict__ win, const float* __restrict__ swk, float* __restrict__ wbin,
                                                       float* __restrict__ abin, float* __restrict__ red, float s, float abs_alpha, float scale,
                                                       const float (&grad)[PATCH_H][PATCH_W], const Geometry& g, int tx, int ty, int lane,
-                                                      float (&gxr)[PATCH_H + 2][PATCH_W + 2])
+                                                      GradWindow3& gxr)
 {
     constexpr int OFF = segment_offset(3, 4), STRIDE = window_stride(3, 4);
     float2 tap_sum[9];
@@ -584,8 +591,8 @@ __device__ __forceinline__ void smorph3_pair_backward(const float* __restrict__ 
             for (int k = 0; k < 9; k++)
             {
                 const float2 c = __ffma2_rn(ged, d[k], __fmul2_rn(ge, e[k]));
-                gxr[rr + 2 - k / 3][2 * jp + 2 - k % 3] += c.x;
-                gxr[rr + 2 - k / 3][2 * jp + 3 - k % 3] += c.y;
+                window_at(gxr, rr + 2 - k / 3, 2 * jp + 2 - k % 3) += c.x;
+                window_at(gxr, rr + 2 - k / 3, 2 * jp + 3 - k % 3) += c.y;
                 tap_sum[k] = __fadd2_rn(tap_sum[k], c);
             }
         }
@@ -611,29 +618,36 @@ __device__ __forceinline__ void smorph3_pair_backward(const float* __restrict__ 
     }
 }
 
-/// smorph3_pair_backward (float) without the maximum: bound_x (the largest s x the thread's pixels can read) plus
-/// bound_w (the largest s w_k) is at least every u_k of the patch, and the caller has checked that scale * (range of x
-/// in the warp's block + range of w) is small, so that 2^(scale (u_k - bound)) of the taps that carry the weight is far
-/// from underflow. The maximum pass goes, and d_k = u_k - bound costs one packed add per tap on top of four centred
-/// window elements per row. The sums S, sum e d and sum e d^2 are relative to the bound instead of the pixel's own
-/// maximum; everything after them is unchanged.
-__device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __restrict__ win, const float* __restrict__ swk, float* __restrict__ wbin,
-                                                              float* __restrict__ abin, float* __restrict__ red, float s, float abs_alpha, float scale,
-                                                              float bound_x, float bound_w, const float (&grad)[PATCH_H][PATCH_W], int tx, int ty,
-                                                              int lane, float (&gxr)[PATCH_H + 2][PATCH_W + 2])
+/// Floats per pair in the table of smorph3_pair_backward_bounded: nine duplicated shifted weights, a pad, and at
+/// BOUNDED_PARAMS the pair's (s scale, |alpha| / scale, 1 / scale^2, widest range of x for which the form is used).
+constexpr int BOUNDED_ROW = 24, BOUNDED_PARAMS = 20;
+/// Range of exponent scales for which smorph3_pair_backward_bounded works in scaled units.
+constexpr float BOUNDED_SCALE_MIN = 1e-6f, BOUNDED_SCALE_MAX = 1e6f;
+
+/// smorph3_pair_backward (float) without the maximum, in units of the exponent. bound_x (the largest s x the thread's
+/// pixels can read) plus bound_w (the largest s w_k) is at least every u_k of the patch, and the caller has checked that
+/// scale * (range of x in the warp's block + range of w) is small, so that 2^(scale (u_k - bound)) of the taps that carry
+/// the weight is far from underflow. The maximum pass goes. The exponent itself,
+///     t_k = scale (u_k - bound) = (scale s x - scale bound_x) + scale (s w_k - bound_w),
+/// takes the place of d_k: one fma per window element and one packed add per tap, the second term read ready-made
+/// (duplicated, for the packed add) from `shifted`, which the chunk's preparation fills. The sums S, sum e t and
+/// sum e t^2 are scale and scale^2 times those of the unscaled form; a common rounding error of the bound shifts every
+/// t_k of a pixel alike and cancels in all three results:
+///     c_k = (g / S) e_k (1 + kappa (t_k - out_t)),   kappa = |alpha| / scale,   out_t = sum e t / S
+///     grad_alpha += (g / S) (sum e t^2 - out_t sum e t) / scale^2.
+__device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __restrict__ win, const float4* __restrict__ shifted4,
+                                                              float* __restrict__ wbin, float* __restrict__ abin, float* __restrict__ red,
+                                                              float4 params, float bound_x, const float* __restrict__ slot, float grad_scale,
+                                                              int tx, int ty, int lane, GradWindow3& gxr)
 {
     constexpr int OFF = segment_offset(3, 4), STRIDE = window_stride(3, 4);
-    float2 tap_sum[9], shifted[9];
+    float2 tap_sum[9];
+    const uint32_t shifted = static_cast<uint32_t>(__cvta_generic_to_shared(shifted4));
 #pragma unroll
-    for (int k = 0; k < 9; k++)
-    {
-        tap_sum[k] = make_float2(0.0f, 0.0f);
-        shifted[k] = make_float2(swk[k] - bound_w, swk[k] - bound_w);
-    }
-    const float minus_bound_x = -bound_x;
+    for (int k = 0; k < 9; k++) tap_sum[k] = make_float2(0.0f, 0.0f);
+    const float slope = params.x, minus_bound = -(fabsf(slope) * bound_x);
+    const float2 kappa2 = make_float2(params.y, params.y);
     float2 alpha_sum = make_float2(0.0f, 0.0f);
-    const float2 scale2 = make_float2(scale, scale), alpha2 = make_float2(abs_alpha, abs_alpha), minus_alpha2 = make_float2(-abs_alpha, -abs_alpha);
-    const float2 one2 = make_float2(1.0f, 1.0f);
 #pragma unroll
     for (int rr = 0; rr < PATCH_H; rr++)
 #pragma unroll
@@ -648,55 +662,68 @@ __device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __res
                 const float* row = win + (ty * PATCH_H + rr + 2 - kh) * STRIDE + tx * PATCH_W + 4 * quad;
                 lds128(seg, row);
                 lds128(seg + 4, row + 4);
-                // d_k = (s x - bound_x) + (s w_k - bound_w): the first difference is exact for the pixels near the bound and
-                // the second is small, so d_k rounds at its own size even when x is far from zero.
                 float centred[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) centred[i] = fmaf(s, seg[base + i], minus_bound_x);
+                for (int i = 0; i < 4; i++) centred[i] = fmaf(slope, seg[base + i], minus_bound);
 #pragma unroll
-                for (int kw = 0; kw < 3; kw++) d[kh * 3 + kw] = __fadd2_rn(make_float2(centred[2 - kw], centred[3 - kw]), shifted[kh * 3 + kw]);
+                for (int kw = 0; kw < 3; kw++) {
+                    float2 sh;
+                    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(sh.x), "=f"(sh.y) : "r"(shifted + 8u * (kh * 3 + kw)));
+                    d[kh * 3 + kw] = __fadd2_rn(make_float2(centred[2 - kw], centred[3 - kw]), sh);
+                }
             }
             float2 sum = make_float2(0.0f, 0.0f), weighted = sum, second = sum;
 #pragma unroll
             for (int k = 0; k < 9; k++)
             {
-                const float2 dk = d[k];
-                const float2 t = __fmul2_rn(dk, scale2);
+                const float2 t = d[k];
                 e[k] = make_float2(ex2_approx(t.x), ex2_approx(t.y));
                 sum = __fadd2_rn(sum, e[k]);
-                d[k] = __fmul2_rn(e[k], dk);   // e_k d_k from here on: exactly zero for excluded taps, whose d_k is -1e30
+                d[k] = __fmul2_rn(e[k], t);   // e_k t_k from here on: exactly zero for excluded taps, whose t_k is hugely negative
                 weighted = __fadd2_rn(weighted, d[k]);
-                second = __ffma2_rn(d[k], dk, second);
+                second = __ffma2_rn(d[k], t, second);
             }
-            // A pixel far outside the image (partial tiles) has no tap at all: S = 0, and it carries no gradient.
-            const float2 inv_sum = make_float2(sum.x > 0.0f ? soft_rcp(sum.x) : 0.0f, sum.y > 0.0f ? soft_rcp(sum.y) : 0.0f);
-            const float2 out_d = __fmul2_rn(weighted, inv_sum);
-            const float2 scaled = __fmul2_rn(make_float2(grad[rr][2 * jp], grad[rr][2 * jp + 1]), inv_sum);
-            const float2 ge = __fmul2_rn(scaled, __ffma2_rn(minus_alpha2, out_d, one2)), ged = __fmul2_rn(scaled, alpha2);
-            const float2 minus_out_d = make_float2(-out_d.x, -out_d.y);
-            alpha_sum = __ffma2_rn(scaled, __ffma2_rn(minus_out_d, weighted, second), alpha_sum);
+            // A pixel far outside the image (partial tiles) has no tap at all: S = 0 and its gradient is zero; the floor
+            // keeps 1 / S finite, so that its products are exact zeros.
+            const float2 inv_sum = make_float2(soft_rcp(fmaxf(sum.x, 1e-30f)), soft_rcp(fmaxf(sum.y, 1e-30f)));
+            const float2 out_t = __fmul2_rn(weighted, inv_sum);
+            // The two gradients come from the thread's slot only now: eight registers less across the tap loops.
+            const float2 raw = *reinterpret_cast<const float2*>(slot + rr * PATCH_W + 2 * jp);
+            const float2 scaled = __fmul2_rn(make_float2(raw.x * grad_scale, raw.y * grad_scale), inv_sum);
+            const float2 ged = __fmul2_rn(scaled, kappa2);
+            const float2 minus_out_t = make_float2(-out_t.x, -out_t.y);
+            const float2 ge = __ffma2_rn(ged, minus_out_t, scaled);
+            alpha_sum = __ffma2_rn(scaled, __ffma2_rn(minus_out_t, weighted, second), alpha_sum);
 #pragma unroll
             for (int k = 0; k < 9; k++)
             {
                 const float2 c = __ffma2_rn(ged, d[k], __fmul2_rn(ge, e[k]));
-                gxr[rr + 2 - k / 3][2 * jp + 2 - k % 3] += c.x;
-                gxr[rr + 2 - k / 3][2 * jp + 3 - k % 3] += c.y;
+                const int r = rr + 2 - k / 3, kw = k % 3;
+                if (kw == 1)
+                {
+                    gxr[r][jp].y += c.x;
+                    gxr[r][jp + 1].x += c.y;
+                }
+                else
+                {
+                    float2& into = gxr[r][kw == 0 ? jp + 1 : jp];
+                    into = __fadd2_rn(into, c);
+                }
                 tap_sum[k] = __fadd2_rn(tap_sum[k], c);
             }
         }
     __syncwarp();
 #pragma unroll
     for (int k = 0; k < 9; k++) red[k * RED_STRIDE + lane] = tap_sum[k].x + tap_sum[k].y;
-    red[9 * RED_STRIDE + lane] = alpha_sum.x + alpha_sum.y;
+    red[9 * RED_STRIDE + lane] = (alpha_sum.x + alpha_sum.y) * params.z;
     __syncwarp();
     float part = 0.0f;
     if (lane < 3 * RED_ROWS)
     {
+        // Three lanes per row, eleven columns each: the last strip ends on the row's pad column, which the kernel keeps zero.
         const float* strip = red + (lane / 3) * RED_STRIDE + (lane % 3) * 11;
-        const int n = (lane % 3) == 2 ? 10 : 11;
 #pragma unroll
-        for (int c = 0; c < 11; c++)
-            if (c < n) part += strip[c];
+        for (int c = 0; c < 11; c++) part += strip[c];
     }
     part += __shfl_down_sync(0xffffffffu, part, 1) + __shfl_down_sync(0xffffffffu, part, 2);
     if (lane < 3 * RED_ROWS && lane % 3 == 0)
@@ -1199,7 +1226,8 @@ struct SmorphBackwardArgs
     const T* soft_inv;  // smooth merge: 1 / sum_i q_i per output pixel
     T* gbeta;           // smooth merge: gradient of beta
     int o_chunk;      // output channels whose weights and bins are staged together
-    int grad_stage;   // byte offset in shared memory of the per-thread staging slots of grad_output, 0 = read it with plain loads
+    int grad_stage;   // byte offset in shared memory of the per-thread slots of grad_output (3 x 3 float kernels)
+    int grad_async;   // grad_output is 16-byte aligned row by row: the slots are filled by cp.async one channel ahead
     T scale;          // 1 / Ci for AVERAGE
     int factorise;    // 5 x 5 and 7 x 7 float kernels: S and N of a pair from the factorised sums where that is safe
     int bounded;      // 3 x 3 float kernels: exponentials relative to a bound of the patch where that is safe
@@ -1434,15 +1462,18 @@ __device__ __forceinline__ void smorph_taps_backward(const float* __restrict__ w
 /// structuring elements and the per-warp gradient bins of a whole chunk live in shared memory, so the loop
 /// over the chunk's output channels runs without a barrier.
 /// SOFT: the smooth channel merge (its own instantiation, so that the other merges keep their register allocation).
-template <typename T, int KH, int KW, bool SOFT>
+/// FAST (3 x 3 float, sum / mean merges, grad_output aligned for cp.async): the channel loop holds nothing but the
+/// staging of the next channel's gradients and the bounded form of the pair, see there.
+template <typename T, int KH, int KW, bool SOFT, bool FAST = false>
 __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) smorph_backward_kernel(const SmorphBackwardArgs<T> a)
 {
+    static_assert(!FAST || (sizeof(T) == 4 && KH == 3 && KW == 3 && !SOFT), "the fast loop is the 3 x 3 float kernel's");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int WARPS = THREADS / 32;
     constexpr int GH = KH > 0 ? PATCH_H + KH - 1 : 1, GW = KH > 0 ? PATCH_W + KW - 1 : 1;
     const Geometry& g = a.g;
-    const int taps = g.taps();
-    const int welems = g.window_elems();
+    const int taps = KH > 0 ? KH * KW : g.taps();   // a compile-time constant for the specialised widths
+    const int welems = KH > 0 ? (TILE_H + KH - 1) * window_stride(KW > 0 ? KW : 1, sizeof(T)) : g.window_elems();
     const int OC = a.o_chunk;
     T* sx = reinterpret_cast<T*>(smem_raw);   // [2][window]: x with -big / +big outside the image
     T* sg = sx + 2 * welems;                   // gradient window
@@ -1458,6 +1489,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     constexpr int FKW = backward_splits<T, KH, KW>() ? KW : 3;
     float2* seb = reinterpret_cast<float2*>(smem_raw + (reinterpret_cast<unsigned char*>(bbins + WARPS * OC + WARPS * RED_ROWS * RED_STRIDE) - smem_raw + 15) / 16 * 16);
     float2* spair = seb + (FACTOR ? OC * taps : 0);
+    // 3 x 3 bounded form: [OC][BOUNDED_ROW], scale (s w_k - Mw) twice per tap (smorph3_pair_backward_bounded).
+    [[maybe_unused]] float* sshift = reinterpret_cast<float*>(smem_raw + (reinterpret_cast<unsigned char*>(spair + OC) - smem_raw + 15) / 16 * 16);
     float4* sea = reinterpret_cast<float4*>(smem_raw + (reinterpret_cast<unsigned char*>(spair + OC) - smem_raw + 15) / 16 * 16)
                   + (threadIdx.x >> 5) * (FactorLayout<FKW>::BYTES / 16);
     const bool factorise = FACTOR && a.factorise != 0;
@@ -1495,6 +1528,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     load_window_signed(has_pos ? sx : nullptr, has_neg ? sx + welems : nullptr, a.x + (static_cast<int64_t>(b) * g.Ci + ci) * plane, g, tile_h0,
                        tile_w0);
     for (int e = threadIdx.x; e < welems; e += THREADS) sg[e] = T(0);
+    for (int e = (threadIdx.x & 31); e < RED_ROWS * RED_STRIDE; e += 32) red[e] = T(0);   // pad columns stay zero
     if (a.grad_stage != 0)
     {
         float4* zero = reinterpret_cast<float4*>(smem_raw + a.grad_stage);
@@ -1518,11 +1552,17 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             for (int j = 0; j < PATCH_W; j++) dst[rr][j] = live[rr][j] ? __ldg(a.gy + at0[rr] + static_cast<int64_t>(o) * plane + j) * a.scale : T(0);
     };
 
-    T gxr[GH][GW];
+    // Register window of grad_input: patch plus halo; column pairs in the 3 x 3 float kernels (GradWindow3).
+    constexpr bool PAIRED_WINDOW = sizeof(T) == 4 && KH == 3 && KW == 3;
+    std::conditional_t<PAIRED_WINDOW, GradWindow3, T[GH][GW]> gxr;
+    auto window = [&](int r, int c) -> T& {
+        if constexpr (PAIRED_WINDOW) return window_at(gxr, r, c);
+        else return gxr[r][c];
+    };
 #pragma unroll
     for (int r = 0; r < GH; r++)
 #pragma unroll
-        for (int c = 0; c < GW; c++) gxr[r][c] = T(0);
+        for (int c = 0; c < GW; c++) window(r, c) = T(0);
 
     // Factorised path: the warp's block of the window (32 x 8 pixels plus halo), the range of x in it (taken once, after
     // the first barrier below) and what the warp's (E, A) buffer holds.
@@ -1576,6 +1616,20 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                         hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
                     }
                     if (lane == 0) spair[oo] = make_float2(hi, hi - lo);
+                    if constexpr (BOUNDED)
+                    {
+                        if (lane < BOUNDED_PARAMS / 2)
+                        {
+                            const float v = lane < 9 ? scale * (sgn * __ldg(wp + lane) - hi) : 0.0f;
+                            reinterpret_cast<float2*>(sshift + oo * BOUNDED_ROW)[lane] = make_float2(v, v);
+                        }
+                        else if (lane == BOUNDED_PARAMS / 2)
+                        {
+                            const bool usable = scale >= BOUNDED_SCALE_MIN && scale <= BOUNDED_SCALE_MAX;
+                            *reinterpret_cast<float4*>(sshift + oo * BOUNDED_ROW + BOUNDED_PARAMS) =
+                                make_float4(sgn * scale, fabsf(al) / scale, 1.0f / (scale * scale), usable ? BOUND_RANGE / scale - (hi - lo) : -1.0f);
+                        }
+                    }
                     if constexpr (FACTOR)
                         for (int k = lane; k < taps; k += 32)
                         {
@@ -1627,195 +1681,282 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                     }
                 }
             }
-            // The 3 x 3 float kernel has no registers to spare for the next channel's gradients (it spills at 128): its
-            // loads are covered by the other warps instead.
-            constexpr bool PREFETCH = !(KH == 3 && sizeof(T) == 4);
-            // Kernels without registers to spare for the next channel's gradients (PREFETCH false) stage them instead: the
-            // thread's two 16-byte rows of the NEXT output channel travel by cp.async into a private slot of shared memory
-            // while the current channel computes, and are read from there when their turn comes (rows outside the image
-            // are never copied and stay zero).
-            [[maybe_unused]] float* slots = nullptr;
-            [[maybe_unused]] int staged = 0;
-            if constexpr (!PREFETCH)
+            // Fast loop of the 3 x 3 float kernels for the usual training case (sum / mean merge, aligned grad_output):
+            // nothing but the staging of the next channel's gradients, one read of the pair's parameter row and the
+            // bounded form; a pair whose exponents are too wide for it takes the max-subtracting form.
+            if constexpr (FAST)
             {
-                if (a.grad_stage != 0)
                 {
-                    slots = reinterpret_cast<float*>(smem_raw + a.grad_stage) + threadIdx.x * (PATCH_H * PATCH_W);
+                    constexpr int BUFFER = THREADS * PATCH_H * PATCH_W;
+                    float* slot_now = reinterpret_cast<float*>(smem_raw + a.grad_stage) + threadIdx.x * (PATCH_H * PATCH_W);
+                    float* slot_next = slot_now + BUFFER;
+                    const bool live0 = live[0][0], live1 = live[1][0];
+                    const float* gy_next = a.gy + at0[0] + static_cast<int64_t>(oc0 + half) * plane;
+                    const int64_t gy_step = static_cast<int64_t>(o_step) * plane;
                     if (half < oc)
                     {
+                        if (live0) cp_async_16(slot_now, gy_next);
+                        if (live1) cp_async_16(slot_now + PATCH_W, gy_next + g.W);
+                    }
+                    constexpr float grad_scale = 1.0f;   // the mean merge's 1 / Ci multiplies the totals instead (below)
+                    const float* row = sshift + half * BOUNDED_ROW;
+                    float* wbin = reinterpret_cast<float*>(wbins) + (warp * OC + half) * 9;
+                    float* abin = reinterpret_cast<float*>(abins) + warp * OC + half;
+                    for (int oo = half; oo < oc; oo += o_step)
+                    {
+                        cp_async_wait_all();
+                        gy_next += gy_step;
+                        if (oo + o_step < oc)
+                        {
+                            if (live0) cp_async_16(slot_next, gy_next);
+                            if (live1) cp_async_16(slot_next + PATCH_W, gy_next + g.W);
+                        }
+                        const float4 params = *reinterpret_cast<const float4*>(row + BOUNDED_PARAMS);
+                        const bool neg = params.x < 0.0f;
+                        const float* win = reinterpret_cast<const float*>(sx) + (neg ? welems : 0);
+                        if (bound_range <= params.w)
+                            smorph3_pair_backward_bounded(win, reinterpret_cast<const float4*>(row), wbin, abin, reinterpret_cast<float*>(red), params,
+                                                          neg ? -local_lo : local_hi, slot_now, grad_scale, tx, ty, lane, gxr);
+                        else
+                        {
+                            float grad[PATCH_H][PATCH_W];
 #pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
+#pragma unroll
+                                for (int j = 0; j < PATCH_W; j++) grad[rr][j] = slot_now[rr * PATCH_W + j] * grad_scale;
+                            smorph3_pair_backward(win, reinterpret_cast<const float*>(sw) + oo * 9, wbin, abin, reinterpret_cast<float*>(red),
+                                                  static_cast<float>(spar[oo * 3]), static_cast<float>(spar[oo * 3 + 1]),
+                                                  static_cast<float>(spar[oo * 3 + 2]), grad, g, tx, ty, lane, gxr);
+                        }
+                        float* swap = slot_now;
+                        slot_now = slot_next;
+                        slot_next = swap;
+                        row += o_step * BOUNDED_ROW;
+                        wbin += o_step * 9;
+                        abin += o_step;
+                    }
+                }
+            }
+            else
+            {
+                // The 3 x 3 float kernel has no registers to spare for the next channel's gradients (it spills at 128): its
+                // loads are covered by the other warps instead.
+                constexpr bool PREFETCH = !(KH == 3 && sizeof(T) == 4);
+                // Kernels without registers to spare for the next channel's gradients (PREFETCH false) keep them in shared
+                // memory instead: the thread's two 16-byte rows of the NEXT output channel travel by cp.async into a private
+                // slot while the current channel computes (rows outside the image are never copied and stay zero), and the
+                // pair's arithmetic reads each pair of gradients from the slot at the point where it needs them. When
+                // grad_output is not 16-byte aligned the slot is filled with plain loads at the top of the iteration.
+                [[maybe_unused]] float* slots = nullptr;
+                [[maybe_unused]] int staged = 0;
+                if constexpr (!PREFETCH)
+                {
+                    slots = reinterpret_cast<float*>(smem_raw + a.grad_stage) + threadIdx.x * (PATCH_H * PATCH_W);
+                    if (a.grad_async != 0 && half < oc)
+                    {
+    #pragma unroll
                         for (int rr = 0; rr < PATCH_H; rr++)
                             if (live[rr][0]) cp_async_16(slots + rr * PATCH_W, a.gy + at0[rr] + static_cast<int64_t>(oc0 + half) * plane);
                     }
                 }
-            }
-            T grad[PATCH_H][PATCH_W];
-            [[maybe_unused]] T next[PREFETCH ? PATCH_H : 1][PREFETCH ? PATCH_W : 1];
-            if constexpr (PREFETCH)
-                if (half < oc) load_grad(oc0 + half, grad);
-            for (int oo = half; oo < oc; oo += o_step)
-            {
-                const int o = oc0 + oo;
+                T grad[PATCH_H][PATCH_W];   // PREFETCH false: a temporary of the steps that need all eight values at once
+                [[maybe_unused]] T next[PREFETCH ? PATCH_H : 1][PREFETCH ? PATCH_W : 1];
                 if constexpr (PREFETCH)
+                    if (half < oc) load_grad(oc0 + half, grad);
+                for (int oo = half; oo < oc; oo += o_step)
                 {
-                    if (oo + o_step < oc) load_grad(o + o_step, next);  // the next channel's gradients arrive while this one computes
-                }
-                else if (slots != nullptr)
-                {
-                    if constexpr (sizeof(T) == 4)
+                    const int o = oc0 + oo;
+                    [[maybe_unused]] float* slot = nullptr;      // PREFETCH false: where this channel's gradients are
+                    [[maybe_unused]] float grad_scale = 1.0f;    // and what they are still to be multiplied by
+                    if constexpr (PREFETCH)
+                    {
+                        if (oo + o_step < oc) load_grad(o + o_step, next);  // the next channel's gradients arrive while this one computes
+                    }
+                    else if (a.grad_async != 0)
                     {
                         cp_async_wait_all();
-                        const float* slot = slots + (staged & 1) * (THREADS * PATCH_H * PATCH_W);
-#pragma unroll
-                        for (int rr = 0; rr < PATCH_H; rr++)
-                        {
-                            const float4 q = *reinterpret_cast<const float4*>(slot + rr * PATCH_W);
-                            grad[rr][0] = q.x * a.scale; grad[rr][1] = q.y * a.scale; grad[rr][2] = q.z * a.scale; grad[rr][3] = q.w * a.scale;
-                        }
+                        slot = slots + (staged & 1) * (THREADS * PATCH_H * PATCH_W);
+                        grad_scale = static_cast<float>(a.scale);
                         staged++;
                         if (oo + o_step < oc)
                         {
                             float* next_slot = slots + (staged & 1) * (THREADS * PATCH_H * PATCH_W);
-#pragma unroll
+    #pragma unroll
                             for (int rr = 0; rr < PATCH_H; rr++)
                                 if (live[rr][0]) cp_async_16(next_slot + rr * PATCH_W, a.gy + at0[rr] + static_cast<int64_t>(o + o_step) * plane);
                         }
                     }
-                }
-                else load_grad(o, grad);
-                const T s = spar[oo * 3], abs_alpha = spar[oo * 3 + 1], scale = spar[oo * 3 + 2];
-                const bool neg = s < T(0);
-                const T* win = sx + (neg ? welems : 0);
-                T* wbin = wbins + (warp * OC + oo) * taps;
-                T* abin = abins + warp * OC + oo;
-                if (winner_takes_all)
-                {
-                    // MAX / MIN: only the channels within 1e-6 of the merged value receive gradient, shared
-                    // equally; the pair's own soft extremum is needed first.
-                    // Same arithmetic as the forward kernel, so that the winning channel reproduces y exactly.
-                    T out[PATCH_H][PATCH_W];
-                    if constexpr (KW == 3)
-                    {
-#pragma unroll
-                        for (int rr = 0; rr < PATCH_H; rr++)
-                        {
-                            T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
-                            smorph3_values(win, sw + oo * taps, 1, s, g, tx, ty, rr, d);
-                            smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
-#pragma unroll
-                            for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
-                        }
-                    }
                     else
                     {
-                        T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
-                        smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
-                    }
-#pragma unroll
-                    for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-                        for (int j = 0; j < PATCH_W; j++)
-                        {
-                            if (!live[rr][j]) continue;
-                            const int64_t at = at0[rr] + static_cast<int64_t>(o) * plane + j;
-                            const T winners = __ldg(a.counts + at);
-                            const T dist = s * out[rr][j] - __ldg(a.y + at);
-                            grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
-                        }
-                }
-                if constexpr (SOFT)
-                {
-                    // Smooth merge: channel i receives g (p_i + beta p_i (c_i - final)), p_i = exp(beta (c_i - ref)) / sum_i q_i,
-                    // and beta receives sum_i p_i (c_i - ref) (c_i - final) g (csrc/cpp/smorph_cpu_kernels.hxx:478, 520-552).
-                    T out[PATCH_H][PATCH_W];
-                    if constexpr (KW == 3)
-                    {
-#pragma unroll
+                        slot = slots;
+    #pragma unroll
                         for (int rr = 0; rr < PATCH_H; rr++)
-                        {
-                            T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
-                            smorph3_values(win, sw + oo * taps, 1, s, g, tx, ty, rr, d);
-                            smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
-#pragma unroll
-                            for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
-                        }
+    #pragma unroll
+                            for (int j = 0; j < PATCH_W; j++)
+                                slot[rr * PATCH_W + j] = live[rr][j] ? static_cast<float>(__ldg(a.gy + at0[rr] + static_cast<int64_t>(o) * plane + j) * a.scale) : 0.0f;
                     }
-                    else
-                    {
-                        T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
-                        smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
-                    }
-                    const T bt = __ldg(a.beta + o);
-                    T beta_sum = T(0);
-#pragma unroll
-                    for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-                        for (int j = 0; j < PATCH_W; j++)
+                    auto grad_from_slot = [&]() {
+                        if constexpr (!PREFETCH)
                         {
-                            if (!live[rr][j]) continue;
-                            const int64_t at = at0[rr] + static_cast<int64_t>(o) * plane + j;
-                            const T c = s * out[rr][j], ref = __ldg(a.soft_ref + at), final = __ldg(a.y + at);
-                            const T p = exp((c - ref) * bt) * __ldg(a.soft_inv + at);
-                            beta_sum = fma(p * (c - ref) * (c - final), grad[rr][j], beta_sum);
-                            grad[rr][j] = grad[rr][j] * fma(bt * p, c - final, p);
+    #pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
+    #pragma unroll
+                                for (int j = 0; j < PATCH_W; j++) grad[rr][j] = slot[rr * PATCH_W + j] * grad_scale;
                         }
-                    beta_sum = warp_sum(beta_sum);
-                    if (lane == 0) bbins[warp * OC + oo] = beta_sum;
-                }
-                if constexpr (backward_splits<T, KH, KW>())
-                {
-                    float centre[PATCH_H][PATCH_W], scaled[PATCH_H][PATCH_W];
-                    bool have_stats = false;
-                    if constexpr (FACTOR)
-                    {
-                        if (factorise)
+                    };
+                    auto grad_to_slot = [&]() {
+                        if constexpr (!PREFETCH)
                         {
-                            const float2 pr = spair[oo];   // (Mw, range of w)
-                            if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE_BACKWARD)
+    #pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
+    #pragma unroll
+                                for (int j = 0; j < PATCH_W; j++) slot[rr * PATCH_W + j] = grad[rr][j];
+                            grad_scale = 1.0f;
+                        }
+                    };
+                    const T s = spar[oo * 3], abs_alpha = spar[oo * 3 + 1], scale = spar[oo * 3 + 2];
+                    const bool neg = s < T(0);
+                    const T* win = sx + (neg ? welems : 0);
+                    T* wbin = wbins + (warp * OC + oo) * taps;
+                    T* abin = abins + warp * OC + oo;
+                    if (winner_takes_all)
+                    {
+                        grad_from_slot();
+                        // MAX / MIN: only the channels within 1e-6 of the merged value receive gradient, shared
+                        // equally; the pair's own soft extremum is needed first.
+                        // Same arithmetic as the forward kernel, so that the winning channel reproduces y exactly.
+                        T out[PATCH_H][PATCH_W];
+                        if constexpr (KW == 3)
+                        {
+    #pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
                             {
-                                if (!(held_s == s && held_scale == scale))
+                                T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+                                smorph3_values(win, sw + oo * taps, 1, s, g, tx, ty, rr, d);
+                                smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+    #pragma unroll
+                                for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
+                            }
+                        }
+                        else
+                        {
+                            T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
+                            smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
+                        }
+    #pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+    #pragma unroll
+                            for (int j = 0; j < PATCH_W; j++)
+                            {
+                                if (!live[rr][j]) continue;
+                                const int64_t at = at0[rr] + static_cast<int64_t>(o) * plane + j;
+                                const T winners = __ldg(a.counts + at);
+                                const T dist = s * out[rr][j] - __ldg(a.y + at);
+                                grad[rr][j] = (dist < T(1e-6) && dist > -T(1e-6)) ? grad[rr][j] / (winners > T(0) ? winners : T(1)) : T(0);
+                            }
+                        grad_to_slot();
+                    }
+                    if constexpr (SOFT)
+                    {
+                        // Smooth merge: channel i receives g (p_i + beta p_i (c_i - final)), p_i = exp(beta (c_i - ref)) / sum_i q_i,
+                        // and beta receives sum_i p_i (c_i - ref) (c_i - final) g (csrc/cpp/smorph_cpu_kernels.hxx:478, 520-552).
+                        T out[PATCH_H][PATCH_W];
+                        if constexpr (KW == 3)
+                        {
+    #pragma unroll
+                            for (int rr = 0; rr < PATCH_H; rr++)
+                            {
+                                T d[9][PATCH_W], e[9][PATCH_W], ref[PATCH_W], inv_sum[PATCH_W], out_d[PATCH_W];
+                                smorph3_values(win, sw + oo * taps, 1, s, g, tx, ty, rr, d);
+                                smorph3_softmax(d, scale, ref, e, inv_sum, out_d);
+    #pragma unroll
+                                for (int j = 0; j < PATCH_W; j++) out[rr][j] = ref[j] + out_d[j];
+                            }
+                        }
+                        else
+                        {
+                            T ref[PATCH_H][PATCH_W], inv_sum[PATCH_H][PATCH_W];
+                            smorph_pair<0, KW>(win, sw + oo * taps, 1, s, scale, g, tx, ty, ref, inv_sum, out);
+                        }
+                        const T bt = __ldg(a.beta + o);
+                        T beta_sum = T(0);
+                        grad_from_slot();
+    #pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+    #pragma unroll
+                            for (int j = 0; j < PATCH_W; j++)
+                            {
+                                if (!live[rr][j]) continue;
+                                const int64_t at = at0[rr] + static_cast<int64_t>(o) * plane + j;
+                                const T c = s * out[rr][j], ref = __ldg(a.soft_ref + at), final = __ldg(a.y + at);
+                                const T p = exp((c - ref) * bt) * __ldg(a.soft_inv + at);
+                                beta_sum = fma(p * (c - ref) * (c - final), grad[rr][j], beta_sum);
+                                grad[rr][j] = grad[rr][j] * fma(bt * p, c - final, p);
+                            }
+                        grad_to_slot();
+                        beta_sum = warp_sum(beta_sum);
+                        if (lane == 0) bbins[warp * OC + oo] = beta_sum;
+                    }
+                    if constexpr (backward_splits<T, KH, KW>())
+                    {
+                        float centre[PATCH_H][PATCH_W], scaled[PATCH_H][PATCH_W];
+                        bool have_stats = false;
+                        if constexpr (FACTOR)
+                        {
+                            if (factorise)
+                            {
+                                const float2 pr = spair[oo];   // (Mw, range of w)
+                                if (x_hi >= x_lo && scale * ((x_hi - x_lo) + pr.y) <= FACTOR_RANGE_BACKWARD)
                                 {
-                                    held_centre = s > 0.0f ? x_hi : -x_lo;
-                                    factor_fill<FKW, true>(win + block_at, sea, s, scale, held_centre, lane, scale * (x_hi - x_lo) > FACTOR_PRECISE);
-                                    held_s = s;
-                                    held_scale = scale;
+                                    if (!(held_s == s && held_scale == scale))
+                                    {
+                                        held_centre = s > 0.0f ? x_hi : -x_lo;
+                                        factor_fill<FKW, true>(win + block_at, sea, s, scale, held_centre, lane, scale * (x_hi - x_lo) > FACTOR_PRECISE);
+                                        held_s = s;
+                                        held_scale = scale;
+                                    }
+                                    // The thread's own largest s x: centre of its linear sums, and with Mw the base of its soft extrema.
+                                    const float local = local_hi >= local_lo ? (s > 0.0f ? local_hi : -local_lo) : held_centre;
+                                    smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, local + pr.x, local - held_centre, held_centre, pr.x,
+                                                               scale * (x_hi - x_lo) > FACTOR_PRECISE, grad, centre, scaled);
+                                    have_stats = true;
                                 }
-                                // The thread's own largest s x: centre of its linear sums, and with Mw the base of its soft extrema.
-                                const float local = local_hi >= local_lo ? (s > 0.0f ? local_hi : -local_lo) : held_centre;
-                                smorph_stats_factored<FKW>(sea, seb + oo * taps, lane, scale, local + pr.x, local - held_centre, held_centre, pr.x,
-                                                           scale * (x_hi - x_lo) > FACTOR_PRECISE, grad, centre, scaled);
-                                have_stats = true;
                             }
                         }
+                        if (!have_stats) smorph_stats_stable<FKW>(win, sw + oo * taps, s, scale, g, tx, ty, grad, centre, scaled);
+                        smorph_taps_backward<FKW>(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, centre, scaled, tx, ty, lane, gxr);
                     }
-                    if (!have_stats) smorph_stats_stable<FKW>(win, sw + oo * taps, s, scale, g, tx, ty, grad, centre, scaled);
-                    smorph_taps_backward<FKW>(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, centre, scaled, tx, ty, lane, gxr);
-                }
-                else if constexpr (KH == 3 && KW == 3)
-                {
-                    bool done = false;
-                    if constexpr (BOUNDED)
+                    else if constexpr (KH == 3 && KW == 3)
                     {
-                        if (bounded)
+                        bool done = false;
+                        if constexpr (BOUNDED)
                         {
-                            const float2 pr = spair[oo];   // (Mw, range of w)
-                            if (scale * (bound_range + pr.y) <= BOUND_RANGE)
+                            if (bounded)
                             {
-                                smorph3_pair_backward_bounded(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale,
-                                                              s > 0.0f ? local_hi : -local_lo, pr.x, grad, tx, ty, lane, gxr);
-                                done = true;
+                                const float4* row = reinterpret_cast<const float4*>(sshift + oo * BOUNDED_ROW);
+                                const float4 params = row[BOUNDED_PARAMS / 4];
+                                if (bound_range <= params.w)
+                                {
+                                    smorph3_pair_backward_bounded(win, row, wbin, abin, red, params, s > 0.0f ? local_hi : -local_lo, slot, grad_scale,
+                                                                  tx, ty, lane, gxr);
+                                    done = true;
+                                }
                             }
                         }
+                        if (!done)
+                        {
+                            grad_from_slot();
+                            smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                        }
                     }
-                    if (!done) smorph3_pair_backward(win, sw + oo * taps, wbin, abin, red, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
-                }
-                else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
-                if constexpr (PREFETCH)
-                {
-#pragma unroll
-                    for (int rr = 0; rr < PATCH_H; rr++)
-#pragma unroll
-                        for (int j = 0; j < PATCH_W; j++) grad[rr][j] = next[rr][j];
+                    else smorph_pair_backward<KH, KW>(win, sw + oo * taps, sg, wbin, abin, s, abs_alpha, scale, grad, g, tx, ty, lane, gxr);
+                    if constexpr (PREFETCH)
+                    {
+    #pragma unroll
+                        for (int rr = 0; rr < PATCH_H; rr++)
+    #pragma unroll
+                            for (int j = 0; j < PATCH_W; j++) grad[rr][j] = next[rr][j];
+                    }
                 }
             }
         }
@@ -1826,6 +1967,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             T total = T(0);
 #pragma unroll
             for (int wp = 0; wp < WARPS; wp++) total += wbins[(wp * OC + oo) * taps + k];
+            if constexpr (FAST) total *= a.scale;
             if (total != T(0)) atomic_add(a.gw + (static_cast<int64_t>(oc0 + oo) * wci + wi) * taps + k, total);
         }
         for (int oo = threadIdx.x; oo < oc; oo += THREADS)
@@ -1833,6 +1975,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
             T total = T(0);
 #pragma unroll
             for (int wp = 0; wp < WARPS; wp++) total += abins[wp * OC + oo];
+            if constexpr (FAST) total *= a.scale;
             if (total != T(0)) atomic_add(a.galpha + (g.identity ? oc0 + oo : static_cast<int64_t>(oc0 + oo) * g.Ci + ci), total);
             if constexpr (SOFT)
             {
@@ -1851,7 +1994,8 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
         for (int r = 0; r < GH; r++)
 #pragma unroll
             for (int c = 0; c < GW; c++)
-                if (gxr[r][c] != T(0)) atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + g.seg_off + c, gxr[r][c]);
+                if (window(r, c) != T(0))
+                    atomic_add(sg + (ty * PATCH_H + r) * g.win_stride + tx * PATCH_W + g.seg_off + c, FAST ? window(r, c) * a.scale : window(r, c));
     }
     __syncthreads();
 
@@ -1898,12 +2042,13 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
     a.bounded = backward_bounds<T, KH, KW, false>() && d.merge != MC_MERGE_SMOOTH;
     if (a.bounded)
     {
-        fixed += 32;
-        per_o += sizeof(float2);
+        fixed += 48;
+        per_o += sizeof(float2) + BOUNDED_ROW * sizeof(float);
     }
     // Staging slots of grad_output for the 3 x 3 float kernel: two buffers of 32 bytes per thread, after everything else.
     constexpr size_t GRAD_SLOTS = 2 * THREADS * PATCH_H * PATCH_W * sizeof(float);
-    const bool stage_grad = sizeof(T) == 4 && KH == 3 && KW == 3 && d.W % 4 == 0 && reinterpret_cast<uintptr_t>(gy) % 16 == 0;
+    const bool stage_grad = sizeof(T) == 4 && KH == 3 && KW == 3;
+    a.grad_async = stage_grad && d.W % 4 == 0 && reinterpret_cast<uintptr_t>(gy) % 16 == 0;
     if (stage_grad) fixed += GRAD_SLOTS + 16;
     if (fixed + per_o > MAX_SHARED_BYTES)
     {
@@ -1926,6 +2071,8 @@ int launch_smorph_backward(const mc_desc& d, const T* x, const T* w, const T* al
         return check_launch("smorph_backward_kernel");
     };
     if (d.merge == MC_MERGE_SMOOTH) return launch(smorph_backward_kernel<T, KH, KW, true>);
+    if constexpr (sizeof(T) == 4 && KH == 3 && KW == 3)
+        if (a.bounded && a.grad_async && d.merge != MC_MERGE_MAX && d.merge != MC_MERGE_MIN) return launch(smorph_backward_kernel<T, KH, KW, false, true>);
     return launch(smorph_backward_kernel<T, KH, KW, false>);
 }
 

@@ -311,7 +311,7 @@ def test_smorph_factorised_forward_matches_double(C, case, merge):
     elif kind == "per_pair":
         a = 3.0 * torch.randn(pairs, generator=g)
     else:
-        values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, 1e-4, 3.0, 25.0, 400.0])
+        values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, -1e-8, 1e-7, 1e-4, 3.0, 25.0, 400.0])
         a = values[torch.randint(0, len(values), pairs, generator=g)]
     a = a.cuda()
     y = C.smorph_forward(x, w, a, merge)
@@ -326,6 +326,8 @@ def test_smorph_factorised_forward_matches_double(C, case, merge):
 @pytest.mark.parametrize("case", [
     # kernel, image, alphas, spread of x
     (3, 224, "uniform", 1.0), (3, 97, "per_pair", 1.0), (3, 61, "extreme", 1.0), (3, 130, "per_pair", 30.0), (3, 100, "offset", 1.0),
+    # widths that are multiples of four take the 3 x 3 kernel's fast channel loop (gradients staged by cp.async)
+    (3, 221, "uniform", 1.0), (3, 125, "offset", 1.0), (3, 93, "per_pair", 30.0),
     (5, 128, "uniform", 1.0), (5, 97, "per_pair", 1.0), (5, 61, "extreme", 1.0), (7, 128, "uniform_negative", 1.0),
     (7, 131, "per_pair", 1.0), (7, 70, "extreme", 3.0), (7, 100, "per_pair", 30.0)])
 @pytest.mark.parametrize("merge", ["sum", "mean", "identity"])
@@ -334,7 +336,8 @@ def test_smorph_factorised_backward_matches_double(C, case, merge):
     sums S and N of a pair from the factorised form wherever the ranges allow it, the 3 x 3 one takes its exponentials
     relative to a bound of the thread's patch instead of the pixel's maximum, and both subtract the maximum elsewhere.
     All must agree with the double kernel, which always subtracts the maximum: interior and border blocks, partial
-    tiles, alpha = 0, signs mixed within one input channel, ranges on both sides of the switch, inputs far from zero."""
+    tiles, alpha = 0 and alphas too small for the bounded form's scaled units, signs mixed within one input channel,
+    ranges on both sides of the switch, inputs far from zero, grad_output rows aligned for cp.async or not."""
     k, hw, kind, spread = case
     g = torch.Generator().manual_seed(4321 + k + hw)
     co, ci = (6, 6) if merge == "identity" else (6, 5)
@@ -353,7 +356,7 @@ def test_smorph_factorised_backward_matches_double(C, case, merge):
     elif kind == "offset":
         a = 2.0 + 0.5 * torch.randn(pairs, generator=g)
     else:
-        values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, 1e-4, 3.0, 25.0, 400.0])
+        values = torch.tensor([-1000.0, -40.0, -6.0, -0.5, 0.0, -1e-8, 1e-7, 1e-4, 3.0, 25.0, 400.0])
         a = values[torch.randint(0, len(values), pairs, generator=g)]
     a = a.cuda()
     y = C.smorph_forward(x, w, a, merge)
