@@ -382,7 +382,7 @@ def run_single(name, device, steps, warmup):
             x, w, a, gy = c["x"].to(device).requires_grad_(True), c["w"].to(device).requires_grad_(True), c["alpha"].to(device).requires_grad_(True), c["gy"].to(device)
             results[f"cfg3 smorph fwd+bwd fp32 mean alpha={alpha:g} (16,32,128,128)x(32,32,7,7)"] = timed(
                 lambda: F.smorph(x, w, a, channel_merge_mode="mean"), gy, c["n_taps"], "smorph_fwdbwd_f32",
-                {"peak_note": "peak of a forward+backward pair: 3 FMA per tap forward, 11 FP32 operations + 1 ex2 per tap backward"})
+                {"peak_note": "peak of a forward+backward pair: 3 FMA per tap forward, 10 FP32 operations + 1 ex2 per tap backward"})
             del x, w, a, gy
     if name in ("cfg4", "all"):
         for op in ("dilation", "erosion"):
