@@ -624,20 +624,22 @@ constexpr int BOUNDED_ROW = 24, BOUNDED_PARAMS = 20;
 /// Range of exponent scales for which smorph3_pair_backward_bounded works in scaled units.
 constexpr float BOUNDED_SCALE_MIN = 1e-6f, BOUNDED_SCALE_MAX = 1e6f;
 
-/// smorph3_pair_backward (float) without the maximum, in units of the exponent. bound_x (the largest s x the thread's
-/// pixels can read) plus bound_w (the largest s w_k) is at least every u_k of the patch, and the caller has checked that
-/// scale * (range of x in the warp's block + range of w) is small, so that 2^(scale (u_k - bound)) of the taps that carry
-/// the weight is far from underflow. The maximum pass goes. The exponent itself,
-///     t_k = scale (u_k - bound) = (scale s x - scale bound_x) + scale (s w_k - bound_w),
+/// smorph3_pair_backward (float) without the maximum, in units of the exponent. The exponentials are taken relative to
+/// centre_x + bound_w, where centre_x is the MIDDLE of the range of s x that the thread's pixels can read and bound_w the
+/// largest s w_k, and the caller has checked that scale * (widest such range in the warp + range of w) is at most
+/// BOUND_RANGE: every exponent then lies within BOUND_RANGE / 2 of zero (plus the range of w below), so no exponential,
+/// sum, reciprocal or product of two of them leaves the normal floats. The maximum pass goes. The exponent itself,
+///     t_k = scale (u_k - centre_x - bound_w) = (scale s x - scale centre_x) + scale (s w_k - bound_w),
 /// takes the place of d_k: one fma per window element and one packed add per tap, the second term read ready-made
 /// (duplicated, for the packed add) from `shifted`, which the chunk's preparation fills. The sums S, sum e t and
-/// sum e t^2 are scale and scale^2 times those of the unscaled form; a common rounding error of the bound shifts every
-/// t_k of a pixel alike and cancels in all three results:
+/// sum e t^2 are scale and scale^2 times those of the unscaled form; the middle of the range keeps |t_k| as small as a
+/// per-thread reference can (the difference sum e t^2 - out_t sum e t of grad_alpha cancels at the size of t^2), and a
+/// common rounding error of the reference shifts every t_k of a pixel alike and cancels in all three results:
 ///     c_k = (g / S) e_k (1 + kappa (t_k - out_t)),   kappa = |alpha| / scale,   out_t = sum e t / S
 ///     grad_alpha += (g / S) (sum e t^2 - out_t sum e t) / scale^2.
 __device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __restrict__ win, const float4* __restrict__ shifted4,
                                                               float* __restrict__ wbin, float* __restrict__ abin, float* __restrict__ red,
-                                                              float4 params, float bound_x, const float* __restrict__ slot, float grad_scale,
+                                                              float4 params, float centre_x, const float* __restrict__ slot, float grad_scale,
                                                               int tx, int ty, int lane, GradWindow3& gxr)
 {
     constexpr int OFF = segment_offset(3, 4), STRIDE = window_stride(3, 4);
@@ -645,7 +647,7 @@ __device__ __forceinline__ void smorph3_pair_backward_bounded(const float* __res
     const uint32_t shifted = static_cast<uint32_t>(__cvta_generic_to_shared(shifted4));
 #pragma unroll
     for (int k = 0; k < 9; k++) tap_sum[k] = make_float2(0.0f, 0.0f);
-    const float slope = params.x, minus_bound = -(fabsf(slope) * bound_x);
+    const float slope = params.x, minus_bound = -(fabsf(slope) * centre_x);
     const float2 kappa2 = make_float2(params.y, params.y);
     float2 alpha_sum = make_float2(0.0f, 0.0f);
 #pragma unroll
@@ -1233,9 +1235,10 @@ struct SmorphBackwardArgs
     int bounded;      // 3 x 3 float kernels: exponentials relative to a bound of the patch where that is safe
 };
 
-/// 3 x 3 float kernels may skip the maximum (smorph3_pair_backward_bounded) while scale * (range of x in the warp's
-/// block + range of w) stays below this many binades.
-constexpr float BOUND_RANGE = 64.0f;
+/// 3 x 3 float kernels may skip the maximum (smorph3_pair_backward_bounded) while scale * (widest range of x in the window
+/// of one thread of the warp + range of w) stays below this many binades: with the reference in the middle of the range the
+/// exponentials stay within 2^-(48 + range of w) .. 2^48 and their sums of squares below 2^65.
+constexpr float BOUND_RANGE = 96.0f;
 template <typename T, int KH, int KW, bool SOFT>
 __host__ __device__ constexpr bool backward_bounds() { return sizeof(T) == 4 && !SOFT && KH == 3 && KW == 3; }
 
@@ -1570,6 +1573,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
     [[maybe_unused]] float x_lo = 0.0f, x_hi = 0.0f, held_s = 0.0f, held_scale = -1.0f, held_centre = 0.0f;
     [[maybe_unused]] bool have_range = false;
     [[maybe_unused]] float local_lo = Limits<float>::inf(), local_hi = -Limits<float>::inf();
+    [[maybe_unused]] float local_mid = 0.0f;   // 3 x 3 bounded form: the middle of the thread's own range of x
     [[maybe_unused]] float bound_range = Limits<float>::inf();   // 3 x 3: range of x in the block, infinite while unknown or unusable
 
     for (int oc0 = o_begin; oc0 < o_end; oc0 += OC)
@@ -1676,6 +1680,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                             local_hi = x_hi;
                             local_lo = x_hi;
                         }
+                        local_mid = 0.5f * local_lo + 0.5f * local_hi;
                         const float widest = from_ordered(__reduce_max_sync(0xffffffffu, to_ordered(local_hi - local_lo)));
                         if (x_hi >= x_lo) bound_range = widest;
                     }
@@ -1716,7 +1721,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                         const float* win = reinterpret_cast<const float*>(sx) + (neg ? welems : 0);
                         if (bound_range <= params.w)
                             smorph3_pair_backward_bounded(win, reinterpret_cast<const float4*>(row), wbin, abin, reinterpret_cast<float*>(red), params,
-                                                          neg ? -local_lo : local_hi, slot_now, grad_scale, tx, ty, lane, gxr);
+                                                          neg ? -local_mid : local_mid, slot_now, grad_scale, tx, ty, lane, gxr);
                         else
                         {
                             float grad[PATCH_H][PATCH_W];
@@ -1937,7 +1942,7 @@ __global__ void __launch_bounds__(THREADS, (sizeof(T) == 8 || KH >= 5) ? 1 : 2) 
                                 const float4 params = row[BOUNDED_PARAMS / 4];
                                 if (bound_range <= params.w)
                                 {
-                                    smorph3_pair_backward_bounded(win, row, wbin, abin, red, params, s > 0.0f ? local_hi : -local_lo, slot, grad_scale,
+                                    smorph3_pair_backward_bounded(win, row, wbin, abin, red, params, s > 0.0f ? local_mid : -local_mid, slot, grad_scale,
                                                                   tx, ty, lane, gxr);
                                     done = true;
                                 }
