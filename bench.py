@@ -471,6 +471,35 @@ def run_case(name, batch, device):
         else:
             args, fn = (x, 0.1 * torch.randn((64, 64, 5, 5), generator=g)), (lambda x, w: F.erosion(x, w, "max"))
         c = {"gy": torch.randn((batch, 64, 224, 224), generator=g)}
+    elif part == "sigma":
+        # sigma_layer on the tensors of configuration 2: its two halves through the paired operator (one fused forward pass)
+        # against the reference's formulation, erosion and dilation called one after the other; timed with CUDA events.
+        c = WL.cfg2(B=batch)
+        x, w, gy = c["x"].to(device), c["w"].to(device), c["gy"].to(device)
+        alpha = torch.zeros((w.shape[0], w.shape[1]), device=device)
+
+        def separate(x, w, a):
+            soft = torch.sigmoid(a.mean(dim=1)).view(1, -1, 1, 1)
+            return F.erosion(x, w, "sum") * (1.0 - soft) + F.dilation(x, w, "sum") * soft
+
+        flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=device)
+        result = {"case": name, "batch": batch}
+        for label, fn in (("paired_ms", lambda x, w, a: F.sigma_layer(x, w, a, "sum")), ("separate_ms", separate)):
+            best = float("inf")
+            for _ in range(4):
+                args = [t.clone().requires_grad_(direction == "bwd") for t in (x, w, alpha)]
+                flush.zero_()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                y = fn(*args)
+                if direction == "bwd":
+                    y.backward(gy)
+                stop.record()
+                torch.cuda.synchronize()
+                best = min(best, start.elapsed_time(stop))
+            result[label] = best
+        emit(result)
+        return
     else:
         raise SystemExit(f"unknown case {name}")
     args = [t.to(device).requires_grad_(direction == "bwd") for t in args]
@@ -508,7 +537,8 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip configurations 1-4")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--case", default=None, help="profiling helper: run one operator twice and exit, e.g. cfg2_fwd, cfg2_bwd, cfg3_fwd, "
-                    "cfg3_bwd, cfg4_fwd, cfg4_bwd, cfg5l2_fwd, cfg5l2_bwd, cfg5l2pp_fwd, cfg5l2pp_bwd, cfg5l3_fwd, cfg5l3_bwd (with --case-batch)")
+                    "cfg3_bwd, cfg4_fwd, cfg4_bwd, cfg5l2_fwd, cfg5l2_bwd, cfg5l2pp_fwd, cfg5l2pp_bwd, cfg5l3_fwd, cfg5l3_bwd (with --case-batch); "
+                    "sigma_fwd / sigma_bwd time sigma_layer through the paired operator against the two separate operators")
     ap.add_argument("--case-batch", type=int, default=4)
     args = ap.parse_args()
 

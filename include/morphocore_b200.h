@@ -76,6 +76,15 @@ typedef struct mc_desc
  * idx (nullable, int32 [B,Co,H,W]) receives (channel << 16) | tap of the winner, MAX / MIN merges only. */
 int mc_morpho_forward(const mc_desc* desc, const void* x, const void* w, void* y, int32_t* idx, void* stream);
 
+/* Dilation AND erosion of one input with one structuring element in a single pass: the two halves of the reference's
+ * sigma_layer composition (morphocore/functional/sigma_layer.py:73-83), which calls erosion(x, w) and dilation(x, w) one
+ * after the other. `w` is the structuring element as the user holds it: the erosion half uses its flipped copy, as
+ * morphocore/functional/erosion.py:89 does, and desc->op is ignored. Results are bit-identical to two mc_morpho_forward
+ * calls. Covers float, square 3 x 3 / 5 x 5 / 7 x 7 structuring elements, shared (not per-sample) weights and borders
+ * that are the same for both operations (replicate, zero, a finite constant); no winner index is produced. Every other
+ * case returns MC_ERR_UNSUPPORTED with nothing launched: run the two passes separately. */
+int mc_morpho_pair_forward(const mc_desc* desc, const void* x, const void* w, void* y_dilation, void* y_erosion, void* stream);
+
 /* Scratch bytes mc_morpho_backward needs: the recomputed winners when idx is NULL for a MAX / MIN merge,
  * otherwise 0. */
 size_t mc_morpho_backward_workspace_bytes(const mc_desc* desc, int have_idx);

@@ -18,7 +18,7 @@ BUILD = os.path.join(PKG, "csrc", "build")
 LIB = os.path.join(PKG, "libmorphocore_b200.so")
 EXT = os.path.join(PKG, "_C.so")
 CUDA_UNITS = ["api.cu", "morpho_forward_f32.cu", "morpho_forward_f64.cu", "morpho_backward_f32.cu", "morpho_backward_f64.cu",
-              "smorph_f32.cu", "smorph_f64.cu", "noalloc.cu"]
+              "smorph_f32.cu", "smorph_f64.cu", "noalloc.cu", "morpho_pair_f32.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

@@ -143,6 +143,17 @@ int mc_morpho_forward(const mc_desc* desc, const void* x, const void* w, void* y
     return morpho_forward<double>(*desc, static_cast<const double*>(x), static_cast<const double*>(w), static_cast<double*>(y), idx, s);
 }
 
+int mc_morpho_pair_forward(const mc_desc* desc, const void* x, const void* w, void* y_dilation, void* y_erosion, void* stream)
+{
+    const int rc = validate(desc, true);
+    if (rc != MC_OK) return rc;
+    if (empty(desc)) return MC_OK;
+    MC_REQUIRE(x); MC_REQUIRE(w); MC_REQUIRE(y_dilation); MC_REQUIRE(y_erosion);
+    if (desc->dtype != MC_F32) return MC_ERR_UNSUPPORTED;
+    return morpho_pair_forward(*desc, static_cast<const float*>(x), static_cast<const float*>(w), static_cast<float*>(y_dilation),
+                               static_cast<float*>(y_erosion), static_cast<cudaStream_t>(stream));
+}
+
 size_t mc_morpho_backward_workspace_bytes(const mc_desc* desc, int have_idx)
 {
     if (desc == nullptr || have_idx) return 0;

@@ -322,6 +322,9 @@ inline int check_launch(const char* what)
 
 // Entry points of the translation units, called by api.cu after validation.
 template <typename T> int morpho_forward(const mc_desc& d, const T* x, const T* w, T* y, int32_t* idx, cudaStream_t stream);
+/// Dilation and erosion (with the flipped structuring element) of one input in one pass; MC_ERR_UNSUPPORTED, with nothing
+/// launched, for the cases the fused kernel does not cover.
+int morpho_pair_forward(const mc_desc& d, const float* x, const float* w, float* y_dilation, float* y_erosion, cudaStream_t stream);
 template <typename T> int morpho_backward(const mc_desc& d, const T* x, const T* w, const int32_t* idx, const T* gy, T* gx, T* gw, void* ws,
                                           cudaStream_t stream);
 template <typename T> int smorph_forward(const mc_desc& d, const T* x, const T* w, const T* alpha, T* y, T* counts, cudaStream_t stream);

@@ -203,6 +203,112 @@ public:
     }
 };
 
+/// dilation(x, w) and erosion(x, w) of the SAME input and structuring element, the two halves of the reference's
+/// sigma_layer (morphocore/functional/sigma_layer.py:73-83). The forward pass is one fused kernel where
+/// mc_morpho_pair_forward covers the case and two mc_morpho_forward calls otherwise; the backward pass is the two
+/// mc_morpho_backward calls the separate operators would make (winners recomputed: no index is kept), their input
+/// gradients added and the erosion's weight gradient flipped back (erosion works on the flipped structuring element,
+/// morphocore/functional/erosion.py:89).
+class MorphoPairFunction : public torch::autograd::Function<MorphoPairFunction>
+{
+public:
+    static torch::autograd::tensor_list forward(torch::autograd::AutogradContext* ctx, torch::Tensor input, torch::Tensor weight, int64_t merge,
+                                                int64_t padding, double padding_value)
+    {
+        const int64_t original_dims = input.dim();
+        torch::Tensor input4d = input_to_4d(input);
+        torch::Tensor weight4d = weight_to_4d(weight);
+        const bool identity = merge == MC_MERGE_IDENTITY;
+        TORCH_CHECK(input4d.size(1) == weight4d.size(1) || identity, "Input channels must match weight input channels");
+        require_cuda(input, "input");
+        require_cuda(weight, "weight");
+        TORCH_CHECK(input.device() == weight.device(), "input and weight must be on the same device");
+        TORCH_CHECK(input.scalar_type() == weight.scalar_type(), "input and weight must have the same dtype");
+        if (identity)
+        {
+            TORCH_CHECK(weight4d.size(0) == input4d.size(1), "Identity mode requires weight.shape[0] == input.shape[1]");
+            TORCH_CHECK(weight4d.size(1) == 1, "Identity mode requires weight.shape[1] == 1");
+        }
+        const c10::cuda::CUDAGuard device_guard(input.device());
+        input4d = input4d.contiguous();
+        weight4d = weight4d.contiguous();
+        const torch::Tensor flipped = weight4d.flip({2, 3}).contiguous();
+
+        mc_desc d = make_desc(input4d, weight4d, MC_OP_DILATION, merge);
+        d.pad_kind = padding == PAD_REPLICATE ? MC_PAD_REPLICATE : MC_PAD_FILL;
+        d.fill = fill_value(MC_OP_DILATION, padding, padding_value, d.dtype == MC_F32);
+        torch::Tensor out_dilation = torch::empty({input4d.size(0), weight4d.size(0), input4d.size(2), input4d.size(3)}, input4d.options());
+        torch::Tensor out_erosion = torch::empty_like(out_dilation);
+        const cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+        {
+            const TraceRange trace("morphocore::morpho_pair_forward");
+            const int rc = mc_morpho_pair_forward(&d, input4d.data_ptr(), weight4d.data_ptr(), out_dilation.data_ptr(), out_erosion.data_ptr(), stream);
+            if (rc == MC_ERR_UNSUPPORTED)
+            {
+                check_status(mc_morpho_forward(&d, input4d.data_ptr(), weight4d.data_ptr(), out_dilation.data_ptr(), nullptr, stream));
+                mc_desc e = d;
+                e.op = MC_OP_EROSION;
+                e.fill = fill_value(MC_OP_EROSION, padding, padding_value, d.dtype == MC_F32);
+                check_status(mc_morpho_forward(&e, input4d.data_ptr(), flipped.data_ptr(), out_erosion.data_ptr(), nullptr, stream));
+            }
+            else check_status(rc);
+        }
+        ctx->save_for_backward({input4d, weight4d, flipped});
+        ctx->saved_data["merge"] = merge;
+        ctx->saved_data["padding"] = padding;
+        ctx->saved_data["padding_value"] = padding_value;
+        ctx->saved_data["input_dims"] = original_dims;
+        ctx->saved_data["weight_dims"] = weight.dim();
+        return {output_to_original(out_dilation, original_dims), output_to_original(out_erosion, original_dims)};
+    }
+
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grad_outputs)
+    {
+        const auto saved = ctx->get_saved_variables();
+        const torch::Tensor& input = saved[0];
+        const torch::Tensor& weight = saved[1];
+        const torch::Tensor& flipped = saved[2];
+        const int64_t merge = ctx->saved_data["merge"].toInt(), padding = ctx->saved_data["padding"].toInt();
+        const double padding_value = ctx->saved_data["padding_value"].toDouble();
+        const c10::cuda::CUDAGuard device_guard(input.device());
+        const cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+
+        torch::Tensor grad_input, grad_weight;
+        for (int op = MC_OP_DILATION; op <= MC_OP_EROSION; op++)
+        {
+            const torch::Tensor& upstream = grad_outputs[op == MC_OP_DILATION ? 0 : 1];
+            if (!upstream.defined()) continue;   // that half of the pair was not used
+            torch::Tensor grad_output = input_to_4d(upstream).contiguous();
+            std::vector<int64_t> expected = input.sizes().vec();
+            expected[1] = weight.size(0);
+            TORCH_CHECK(grad_output.sizes() == c10::IntArrayRef(expected), "grad_output shape mismatch: expected [", c10::IntArrayRef(expected),
+                        "] but got [", grad_output.sizes(), "]");
+            TORCH_CHECK(grad_output.device() == input.device(), "grad_output must be on the same device as input");
+            TORCH_CHECK(grad_output.scalar_type() == input.scalar_type(), "grad_output must have the same dtype as input");
+            mc_desc d = make_desc(input, weight, op, merge);
+            d.pad_kind = padding == PAD_REPLICATE ? MC_PAD_REPLICATE : MC_PAD_FILL;
+            d.fill = fill_value(op, padding, padding_value, d.dtype == MC_F32);
+            const torch::Tensor& kernel_weight = op == MC_OP_DILATION ? weight : flipped;
+            torch::Tensor gx = torch::empty_like(input), gw = torch::empty_like(weight);
+            const size_t ws_bytes = mc_morpho_backward_workspace_bytes(&d, 0);
+            torch::Tensor workspace;
+            if (ws_bytes > 0) workspace = torch::empty({static_cast<int64_t>(ws_bytes)}, input.options().dtype(torch::kByte));
+            const TraceRange trace("morphocore::morpho_backward");
+            check_status(mc_morpho_backward(&d, input.data_ptr(), kernel_weight.data_ptr(), nullptr, grad_output.data_ptr(), gx.data_ptr(), gw.data_ptr(),
+                                            workspace.defined() ? workspace.data_ptr() : nullptr, ws_bytes, stream));
+            if (op == MC_OP_EROSION) gw = gw.flip({2, 3});
+            grad_input = grad_input.defined() ? grad_input + gx : gx;
+            grad_weight = grad_weight.defined() ? grad_weight + gw : gw;
+        }
+        if (grad_input.defined())
+        {
+            grad_input = output_to_original(grad_input, ctx->saved_data["input_dims"].toInt());
+            if (ctx->saved_data["weight_dims"].toInt() == 2) grad_weight = grad_weight.squeeze(0).squeeze(0);
+        }
+        return {grad_input, grad_weight, torch::Tensor(), torch::Tensor(), torch::Tensor()};
+    }
+};
+
 /// One alpha per (o, i) pair, a single value being shared by all (csrc/cpp/smorph_cpu_kernels.hxx:643-649).
 torch::Tensor pair_alphas(const torch::Tensor& alpha, int64_t merge, int64_t out_channels, int64_t in_channels)
 {
@@ -419,6 +525,25 @@ torch::Tensor erosion(torch::Tensor input, torch::Tensor weight, int64_t merge, 
                                  save_indices, noise_scale);
 }
 
+/// Extension (not an operator of the reference): both halves of sigma_layer at once. MAX / MIN merges that keep their
+/// winner indices for the backward pass run the two separate operators, which is what saves them.
+std::tuple<torch::Tensor, torch::Tensor> dilation_erosion(torch::Tensor input, torch::Tensor weight, int64_t merge, int64_t padding, double padding_value,
+                                                          bool save_indices)
+{
+    if (is_reduced(input))
+    {
+        auto [d, e] = dilation_erosion(input.to(torch::kFloat), widen(weight, input, "weight"), merge, padding, padding_value, save_indices);
+        return {d.to(input.scalar_type()), e.to(input.scalar_type())};
+    }
+    merge = checked_merge(merge);
+    padding = checked_padding(padding);
+    if (save_indices && (merge == MC_MERGE_MAX || merge == MC_MERGE_MIN))
+        return {dilation(input, weight, merge, padding, padding_value, true, 0.0),
+                erosion(input, weight.flip({-2, -1}), merge, padding, padding_value, true, 0.0)};
+    const auto out = MorphoPairFunction::apply(input, weight, merge, padding, padding_value);
+    return {out[0], out[1]};
+}
+
 torch::Tensor smorph(torch::Tensor input, torch::Tensor weight, torch::Tensor alpha, int64_t merge)
 {
     TORCH_CHECK(merge >= 0 && merge <= MC_MERGE_IDENTITY && merge != MC_MERGE_SMOOTH, "Unsupported merge operation for smorph");
@@ -445,6 +570,7 @@ TORCH_LIBRARY(morphocore, m)
           "float noise_scale=0.) -> Tensor");
     m.def("smorph(Tensor input, Tensor weight, Tensor alpha, int merge) -> Tensor");
     m.def("smorph_scm(Tensor input, Tensor weight, Tensor alpha, Tensor beta) -> Tensor");
+    m.def("dilation_erosion(Tensor input, Tensor weight, int merge, int padding, float padding_value=0., bool save_indices=True) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(morphocore, CompositeImplicitAutograd, m)
@@ -453,4 +579,5 @@ TORCH_LIBRARY_IMPL(morphocore, CompositeImplicitAutograd, m)
     m.impl("erosion", &erosion);
     m.impl("smorph", &smorph);
     m.impl("smorph_scm", &smorph_scm);
+    m.impl("dilation_erosion", &dilation_erosion);
 }

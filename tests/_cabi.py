@@ -57,6 +57,18 @@ def morpho_forward(op, x, w, merge="sum", padding="replicate", padding_value=0.0
     return (y, idx) if with_index else y
 
 
+def morpho_pair_forward(x, w, merge="sum", padding="replicate", padding_value=0.0):
+    """Dilation and erosion (flipped structuring element) of x in one pass; None when the case is not covered."""
+    d = make_desc("dilation", x, w, merge, padding, padding_value)
+    yd = torch.empty((d.B, d.Co, d.H, d.W), dtype=x.dtype, device=x.device)
+    ye = torch.empty_like(yd)
+    rc = lib.mc_morpho_pair_forward(ctypes.byref(d), ptr(x), ptr(w), ptr(yd), ptr(ye), stream())
+    if rc == -2:   # MC_ERR_UNSUPPORTED
+        return None
+    check(rc)
+    return yd, ye
+
+
 def morpho_backward(op, x, w, gy, merge="sum", padding="replicate", padding_value=0.0, idx=None):
     d = make_desc(op, x, w, merge, padding, padding_value)
     gx = torch.empty_like(x)

@@ -274,6 +274,51 @@ def test_compositions_against_the_oracle(F):
     np.testing.assert_allclose(w1r.grad.cpu().numpy(), flip(g_w1), rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("case", [
+    # dtype, kernel, width, merge, padding, save_indices: the first rows run the fused forward kernel, the others its fallbacks
+    (torch.float32, 3, 36, "sum", "replicate", True), (torch.float32, 5, 64, "mean", "zero", True), (torch.float32, 7, 40, "identity", "constant", True),
+    (torch.float32, 3, 36, "max", "replicate", False), (torch.float32, 3, 36, "min", "replicate", True), (torch.float32, 3, 35, "sum", "replicate", True),
+    (torch.float32, 5, 36, "sum", "geodesic", True), (torch.float32, 4, 36, "sum", "replicate", True), (torch.float64, 3, 36, "sum", "replicate", True)])
+def test_sigma_layer_through_the_paired_operator(F, case):
+    """sigma_layer computes its two halves with one operator (torch.ops.morphocore.dilation_erosion: one fused pass over x where
+    mc_morpho_pair_forward covers the case). Values must equal the reference's formulation, erosion(x, w) and dilation(x, w)
+    called one after the other (morphocore/functional/sigma_layer.py:73-83), bit for bit, and the gradients of x, w and alpha
+    must agree with those of that formulation to summation order."""
+    dtype, k, width, merge, padding, save_indices = case
+    g = torch.Generator().manual_seed(31 + k + width)
+    co, ci = (5, 5) if merge == "identity" else (5, 3)
+    x = torch.randn((2, ci, 30, width), generator=g, dtype=dtype).cuda()
+    w = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, k, k), generator=g, dtype=dtype)).cuda()
+    alpha = torch.randn((co, ci), generator=g, dtype=dtype).cuda()
+    gy = torch.randn((2, co, 30, width), generator=g, dtype=dtype).cuda()
+    kwargs = dict(channel_merge_mode=merge, padding_mode=padding, save_indices=save_indices, padding_value=0.25)
+
+    def reference_form(x, w, alpha):
+        soft = torch.sigmoid(alpha.mean(dim=1)).view(1, -1, 1, 1)
+        return F.erosion(x, w, **kwargs) * (1.0 - soft) + F.dilation(x, w, **kwargs) * soft
+
+    grads = []
+    outs = []
+    for fn in (lambda x, w, a: F.sigma_layer(x, w, a, **kwargs), reference_form):
+        xr, wr, ar = (t.clone().requires_grad_(True) for t in (x, w, alpha))
+        y = fn(xr, wr, ar)
+        y.backward(gy)
+        outs.append(y.detach())
+        grads.append((xr.grad, wr.grad, ar.grad))
+    assert torch.equal(outs[0], outs[1])
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-12, atol=1e-12)
+    for got, want in zip(grads[0], grads[1]):
+        torch.testing.assert_close(got, want, **tol)
+    # one half alone: the other half's gradient is simply absent
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    dil, _ = torch.ops.morphocore.dilation_erosion(xr, wr, F.merge_enum.str_to_merge(merge), F.merge_enum.str_to_padding(padding), 0.25, save_indices)
+    dil.backward(gy)
+    xs, ws = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    F.dilation(xs, ws, **kwargs).backward(gy)
+    torch.testing.assert_close(xr.grad, xs.grad, **tol)
+    torch.testing.assert_close(wr.grad, ws.grad, **tol)
+
+
 def test_compositions(F):
     """opening / closing with one shared structuring element and geodesic padding are idempotent and
     (anti-)extensive; sigma_layer blends erosion and dilation (the reference's

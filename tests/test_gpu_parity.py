@@ -181,6 +181,33 @@ def test_negative_zero_inputs(C, dtype):
             np.testing.assert_allclose(gw.cpu().numpy(), wgw, **grad_tol(dtype, 100), err_msg=str((op, merge)))
 
 
+@pytest.mark.parametrize("merge", ["sum", "mean", "max", "min", "identity"])
+@pytest.mark.parametrize("k", [3, 5, 7])
+def test_fused_dilation_erosion_pass_is_bit_identical(C, merge, k):
+    """mc_morpho_pair_forward (the two halves of sigma_layer, morphocore/functional/sigma_layer.py:73-83, in one pass) against
+    two mc_morpho_forward calls, erosion with the flipped structuring element as morphocore/functional/erosion.py:89 passes it:
+    bit-identical outputs for every merge and border it covers, partial tiles and a width that is not a multiple of four
+    included; the cases it does not cover answer MC_ERR_UNSUPPORTED and launch nothing."""
+    g = torch.Generator().manual_seed(77 + k)
+    co, ci = (6, 6) if merge == "identity" else (5, 7)
+    for shape, padding, value in (((2, ci, 70, 100), "replicate", 0.0), ((1, ci, 33, 68), "zero", 0.0), ((2, ci, 64, 64), "constant", 0.25)):
+        x = torch.randn(shape, generator=g).cuda()
+        w = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, k, k), generator=g)).cuda()
+        pair = C.morpho_pair_forward(x, w, merge, padding, value)
+        assert pair is not None
+        yd = C.morpho_forward("dilation", x, w, merge, padding, value)
+        ye = C.morpho_forward("erosion", x, torch.flip(w, dims=(-2, -1)).contiguous(), merge, padding, value)
+        assert torch.equal(pair[0], yd)
+        assert torch.equal(pair[1], ye)
+    x = torch.randn((1, ci, 40, 40), generator=g).cuda()
+    w = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, k, k), generator=g)).cuda()
+    assert C.morpho_pair_forward(x, w, merge, "geodesic") is None                       # the fill value differs between the two
+    assert C.morpho_pair_forward(x.double(), w.double(), merge) is None                 # float only
+    w4 = (0.3 * torch.randn((co, 1 if merge == "identity" else ci, 4, 4), generator=g)).cuda()
+    assert C.morpho_pair_forward(x, w4, merge) is None                                  # 3 x 3, 5 x 5, 7 x 7 only
+    assert C.morpho_pair_forward(x[..., :37].contiguous(), w, merge) is None            # rows that TMA cannot address (pitch not 16 bytes)
+
+
 def test_per_sample_weights(C):
     """weight_batch_stride: one structuring element per batch element equals running each element alone,
     and grad_weight is the sum over the batch."""
