@@ -400,6 +400,44 @@ def test_smorph_factorised_backward_matches_double(C, case, merge):
     torch.testing.assert_close(ga.double(), ra, rtol=1e-4 * amp, atol=1e-4 * amp * float(ra.abs().max()))
 
 
+def test_smorph_3x3_random_shapes_against_double(C):
+    """Sixty random 3 x 3 problems (1-3 images of up to 90 x 160 pixels, widths that are multiples of four so that the fast
+    channel loop of the backward kernel runs, 1-9 channels, sum / mean / identity merges, inputs spread over 0.1 to 30 units
+    around 0, 50 or -200, alphas up to +-25 with zeros mixed in): the float kernels against the double kernels. The parameter
+    gradients are sums over the image of terms of both signs, so their error is held against the sum of the terms'
+    magnitudes (the same backward pass on |grad_output|), the input gradient and the output against their largest element."""
+    import random
+    random.seed(5)
+    g = torch.Generator().manual_seed(5)
+    for _ in range(60):
+        merge = random.choice(["sum", "mean", "identity"])
+        B, H, W = random.randint(1, 3), random.randint(3, 90), 4 * random.randint(1, 40)
+        ci = random.randint(1, 9)
+        co = ci if merge == "identity" else random.randint(1, 9)
+        spread, offset = random.choice([0.1, 1.0, 1.0, 5.0, 30.0]), random.choice([0.0, 0.0, 50.0, -200.0])
+        x = (offset + spread * torch.randn((B, ci, H, W), generator=g)).cuda()
+        w = (random.choice([0.05, 0.3, 2.0]) * torch.randn((co, 1 if merge == "identity" else ci, 3, 3), generator=g)).cuda()
+        pairs = (co,) if merge == "identity" else (co, ci)
+        a = (random.choice([0.5, 2.0, 8.0]) * torch.randn(pairs, generator=g)).cuda()
+        if random.random() < 0.3:
+            a[(torch.rand(pairs, generator=g) < 0.3).cuda()] = 0.0
+        gy = torch.randn((B, co, H, W), generator=g).cuda()
+        y = C.smorph_forward(x, w, a, merge)
+        yd = C.smorph_forward(x.double(), w.double(), a.double(), merge)
+        gx, gw, ga = C.smorph_backward(x, w, a, y, gy, merge)
+        rx, rw, ra = C.smorph_backward(x.double(), w.double(), a.double(), yd, gy.double(), merge)
+        _, sw, sa = C.smorph_backward(x.double(), w.double(), a.double(), yd, gy.double().abs(), merge)
+        where = f"{merge} {(B, ci, co, H, W)} spread {spread} offset {offset}"
+        amp = max(1.0, float(a.abs().max()) / 10.0)   # rounding of exp() is multiplied by |alpha| in the gradients
+        for t in (y, gx, gw, ga):
+            assert torch.isfinite(t).all(), where
+        scale = ci if merge == "sum" else 1
+        assert float((y.double() - yd).abs().max()) <= 1e-4 * float(yd.abs().max()) + 1e-5 * scale * max(1.0, spread), where
+        assert float((gx.double() - rx).abs().max()) <= 1e-4 * amp * max(float(rx.abs().max()), 1e-6), where
+        assert float((gw.double() - rw).abs().max()) <= 1e-4 * amp * float(sw.abs().max()), where
+        assert float((ga.double() - ra).abs().max()) <= 1e-4 * amp * float(sa.abs().max()), where
+
+
 @pytest.mark.parametrize("merge", ["max", "min"])
 @pytest.mark.parametrize("k", [3, 5])
 def test_smorph_winner_merges_at_scale(C, merge, k):
